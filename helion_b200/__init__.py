@@ -1,0 +1,16 @@
+"""B200-native (sm_100a) fused linear-cross-entropy: a drop-in for the reference's
+``tritium.linear_cross_entropy`` / ``tritium.linear_cross_entropy_backward``.
+
+Importing this package needs no GPU; calling an op needs libhelion_lce.so (built in-tree by
+``helion_b200.build``) and an sm_100 device. There is no CPU or torch fallback.
+"""
+
+from .install import install, uninstall
+from .ops import linear_cross_entropy, linear_cross_entropy_backward
+
+__all__ = [
+    "install",
+    "linear_cross_entropy",
+    "linear_cross_entropy_backward",
+    "uninstall",
+]

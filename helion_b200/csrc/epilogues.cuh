@@ -1,0 +1,252 @@
+// Epilogue functors shared by the tcgen05 GEMM core and the CUDA-core (SIMT) GEMM core.
+//
+// Both cores hand an accumulator tile to the functor the same way: one thread owns one row of the
+// tile and receives it 32 consecutive fp32 columns at a time.
+//   begin(state, params, tile)            once per tile, before any column arrives
+//   chunk(state, params, tile, col0, v)   v[j] = D[row, col0 + j], col0 relative to the tile
+//   end(state, params, tile)              once per tile, after the last chunk
+// Row reductions are therefore thread-local: no shuffles, no shared memory.
+#pragma once
+
+#include "gemm_tc.cuh"
+
+namespace lce {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+template <class T> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct Cvt<__half> {
+    static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+template <> struct Cvt<float> {
+    static __device__ __forceinline__ float to_f(float x) { return x; }
+    static __device__ __forceinline__ float from_f(float x) { return x; }
+};
+
+__device__ __forceinline__ long long load_target(const void* tgt, int is_i64, long long i) {
+    return is_i64 ? static_cast<const long long*>(tgt)[i]
+                  : static_cast<long long>(static_cast<const int*>(tgt)[i]);
+}
+
+// Stores 32 consecutive values of one row. Vectorised (16-byte) when the whole chunk is in
+// bounds and the destination is 16-byte aligned; element-wise on the ragged edge.
+template <class T>
+__device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int ncols_valid) {
+    constexpr int kPerVec = 16 / sizeof(T);
+    if (ncols_valid >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32 / kPerVec; ++i) {
+            alignas(16) T tmp[kPerVec];
+#pragma unroll
+            for (int j = 0; j < kPerVec; ++j) tmp[j] = Cvt<T>::from_f(v[i * kPerVec + j]);
+            *reinterpret_cast<uint4*>(dst + i * kPerVec) = *reinterpret_cast<const uint4*>(tmp);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < ncols_valid) dst[j] = Cvt<T>::from_f(v[j]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward: per (vocab tile, row) partial softmax statistics.
+//   partial[(n_tile*3 + 0) * row_stride + row] = max_j z[row, j]
+//   partial[(n_tile*3 + 1) * row_stride + row] = sum_j exp(z[row, j] - max)
+//   partial[(n_tile*3 + 2) * row_stride + row] = z[row, target] if the target falls in this tile
+//                                                else -inf
+// Columns at or beyond `vocab` (zero-filled by TMA) are masked to -inf. The same three numbers
+// per block are what the reference's partial-forward kernel emits
+// (tritium/ops/cross_entropy.py:235-248).
+// ---------------------------------------------------------------------------------------------
+struct EpiStats {
+    struct Params {
+        const void* tgt;
+        int tgt_i64;
+        int rows;               // valid rows
+        int vocab;              // valid columns (local shard width)
+        long long vocab_start;  // global index of local column 0
+        float* partial;
+        long long row_stride;
+    };
+    struct State {
+        float m, s, t;
+        int tcol;  // target column relative to the tile, or -1
+        int row;
+    };
+    static __device__ __forceinline__ void begin(State& st, const Params& p, const TileCtx& tc) {
+        st.row = tc.m_tile * kBM + tc.row_in_tile;
+        st.m = -INFINITY;
+        st.s = 0.f;
+        st.t = -INFINITY;
+        st.tcol = -1;
+        if (st.row < p.rows) {
+            const long long rel = load_target(p.tgt, p.tgt_i64, st.row) - p.vocab_start -
+                                  static_cast<long long>(tc.n_tile) * tc.bn;
+            if (rel >= 0 && rel < tc.bn && rel + static_cast<long long>(tc.n_tile) * tc.bn < p.vocab)
+                st.tcol = static_cast<int>(rel);
+        }
+    }
+    static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
+                                                 int col0, float (&v)[32]) {
+        const int gcol0 = tc.n_tile * tc.bn + col0;
+        if (gcol0 >= p.vocab) return;
+        if (gcol0 + 32 > p.vocab) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (gcol0 + j >= p.vocab) v[j] = -INFINITY;
+        }
+        if (st.tcol >= col0 && st.tcol < col0 + 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j == st.tcol) st.t = v[j];
+        }
+        float cm = v[0];
+#pragma unroll
+        for (int j = 1; j < 32; ++j) cm = fmaxf(cm, v[j]);
+        const float nm = fmaxf(st.m, cm);
+        // nm == -inf only if every logit so far is -inf; keep the exponent arguments finite
+        const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += ptx::ex2(fmaf(v[j], kLog2e, -nm2));
+        st.s = st.s * ptx::ex2(fmaf(st.m, kLog2e, -nm2)) + acc;
+        st.m = nm;
+    }
+    static __device__ __forceinline__ void end(State& st, const Params& p, const TileCtx& tc) {
+        if (st.row < p.rows) {
+            float* base = p.partial + static_cast<long long>(tc.n_tile) * 3 * p.row_stride + st.row;
+            base[0] = st.m;
+            base[p.row_stride] = st.s;
+            base[2 * p.row_stride] = st.t;
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Backward step 1: recompute a logits tile and turn it into the logit gradient
+//   G[row, col] = (exp(z - lse[row]) - [col == target[row]]) * rowscale[row]
+// rounded to the input dtype (the reference rounds G the same way before its two GEMMs,
+// tritium/ops/cross_entropy.py:361-367) and written to the band buffer g[row * ldg + col].
+// rowscale already holds grad_out / valid_count (or grad_out, or grad_out[row]) and is 0 for
+// ignored rows. The GEMM runs on a sub-block (rows row_off.., local columns col_off..).
+// ---------------------------------------------------------------------------------------------
+template <class T>
+struct EpiGrad {
+    struct Params {
+        const void* tgt;
+        int tgt_i64;
+        int rows;               // valid rows of this block
+        int cols;               // valid columns of this block
+        int row_off;            // first global row of the block
+        long long col_global0;  // global vocab index of block column 0
+        const float* lse;
+        const float* rowscale;
+        T* g;
+        long long ldg;
+    };
+    struct State {
+        float l2, sc;
+        int tcol, row;
+    };
+    static __device__ __forceinline__ void begin(State& st, const Params& p, const TileCtx& tc) {
+        st.row = tc.m_tile * kBM + tc.row_in_tile;
+        st.tcol = -1;
+        st.sc = 0.f;
+        st.l2 = 0.f;
+        if (st.row < p.rows) {
+            const int grow = p.row_off + st.row;
+            st.sc = p.rowscale[grow];
+            st.l2 = p.lse[grow] * kLog2e;
+            const long long rel = load_target(p.tgt, p.tgt_i64, grow) - p.col_global0 -
+                                  static_cast<long long>(tc.n_tile) * tc.bn;
+            if (rel >= 0 && rel < tc.bn) st.tcol = static_cast<int>(rel);
+        }
+    }
+    static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
+                                                 int col0, float (&v)[32]) {
+        if (st.row >= p.rows) return;
+        const int bcol0 = tc.n_tile * tc.bn + col0;  // column inside the block
+        if (bcol0 >= p.cols) return;
+        if (st.sc == 0.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = ptx::ex2(fmaf(v[j], kLog2e, -st.l2)) * st.sc;
+            if (st.tcol >= col0 && st.tcol < col0 + 32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j == st.tcol) v[j] -= st.sc;
+            }
+        }
+        store_row32<T>(p.g + static_cast<long long>(st.row) * p.ldg + bcol0, v, p.cols - bcol0);
+    }
+    static __device__ __forceinline__ void end(State&, const Params&, const TileCtx&) {}
+};
+
+// ---------------------------------------------------------------------------------------------
+// Backward steps 2 and 3: store a plain GEMM result (dW block or dX block), optionally summed
+// over several launches in a fixed order through an fp32 scratch buffer:
+//   kStoreDirect  out = acc                      (the contraction was complete in one launch)
+//   kStoreFirst   scratch = acc                  (first partial sum)
+//   kStoreAccum   scratch += acc
+//   kStoreLast    out = scratch + acc            (rounded to the output dtype once, at the end)
+// The launches of one sum run in stream order, so the summation order - and the result - is the
+// same on every run (this is the deterministic split-K). The scratch buffer is private to the
+// library, so it is laid out for coalescing, not as a matrix: float4 index
+//   ((tile * bn/4 + col/4) * 128 + row_in_tile).
+// ---------------------------------------------------------------------------------------------
+enum StoreMode { kStoreDirect = 0, kStoreFirst = 1, kStoreAccum = 2, kStoreLast = 3 };
+
+template <class T>
+struct EpiStore {
+    struct Params {
+        T* out;
+        long long ldo;
+        int rows, cols;  // valid extent of the output block
+        float* scratch;
+        int mode;
+    };
+    struct State {
+        int row;
+    };
+    static __device__ __forceinline__ void begin(State& st, const Params&, const TileCtx& tc) {
+        st.row = tc.m_tile * kBM + tc.row_in_tile;
+    }
+    static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
+                                                 int col0, float (&v)[32]) {
+        const int gcol0 = tc.n_tile * tc.bn + col0;
+        if (p.mode != kStoreDirect) {
+            float4* sp = reinterpret_cast<float4*>(p.scratch) +
+                         ((static_cast<long long>(tc.m_tile) * tc.n_tiles + tc.n_tile) * (tc.bn / 4) +
+                          col0 / 4) * kBM + tc.row_in_tile;
+            if (p.mode != kStoreFirst) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 o = sp[i * kBM];
+                    v[4 * i + 0] += o.x;
+                    v[4 * i + 1] += o.y;
+                    v[4 * i + 2] += o.z;
+                    v[4 * i + 3] += o.w;
+                }
+            }
+            if (p.mode != kStoreLast) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    sp[i * kBM] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                return;
+            }
+        }
+        if (st.row >= p.rows || gcol0 >= p.cols) return;
+        store_row32<T>(p.out + static_cast<long long>(st.row) * p.ldo + gcol0, v, p.cols - gcol0);
+    }
+    static __device__ __forceinline__ void end(State&, const Params&, const TileCtx&) {}
+};
+
+}  // namespace lce

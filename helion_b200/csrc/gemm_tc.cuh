@@ -1,0 +1,264 @@
+// Persistent, warp-specialised tcgen05 GEMM core for sm_100a.
+//
+//   D[m, n] = sum_k A[m, k] * B[n, k]        (fp32 accumulation in tensor memory)
+//
+// Operands are 16-bit (bf16 or fp16) and arrive through TMA tensor maps into 128-byte-swizzled
+// shared memory. Either operand may be K-major (k contiguous in global memory) or MN-major
+// (m resp. n contiguous), so that X·Wᵀ, G·W and Gᵀ·X all run on this one main loop without a
+// transposed copy of anything. The result never leaves the chip as a matrix: an epilogue functor
+// receives every 128 x BN accumulator tile as "one thread = one row, 32 columns at a time" and
+// decides what reaches global memory (softmax statistics, the logit-gradient band, dX, dW).
+//
+// CTA layout (192 threads):
+//   warp 0      TMA producer   (one elected lane)
+//   warp 1      tensor-memory allocator + tcgen05.mma issuer (one elected lane)
+//   warps 2-5   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
+// Pipelines: STAGES-deep smem ring (full/empty mbarriers) between producer and issuer, and two
+// accumulator buffers in TMEM (tmem_full/tmem_empty) so the epilogue of tile i overlaps the main
+// loop of tile i+1. Tiles are dealt round-robin to a grid of (at most) one CTA per SM.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace lce {
+
+constexpr int kBM = 128;      // accumulator tile rows  (= TMEM lanes)
+constexpr int kBK = 64;       // k elements per pipeline stage (= one 128-byte swizzle row)
+constexpr int kUmmaK = 16;    // k elements per tcgen05.mma for 16-bit operands
+constexpr int kGemmThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+// error codes written to the device status word
+constexpr int kDevErrProducerTimeout = 101;
+constexpr int kDevErrMmaTimeout = 102;
+constexpr int kDevErrEpilogueTimeout = 103;
+
+struct TileCtx {
+    int m_tile;       // tile row index
+    int n_tile;       // tile column index
+    int n_tiles;      // tile columns in the problem
+    int row_in_tile;  // 0..127, the row this thread owns
+    int bn;           // tile width in columns
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int kABytes = kBM * kBK * 2;
+    static constexpr int kBBytes = BN * kBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierBytes = 256;
+    // 1024 bytes of slack so the ring can be aligned to the swizzle atom by hand
+    static constexpr int kTotalBytes = STAGES * kStageBytes + kBarrierBytes + 1024;
+};
+
+// m_fastest: consecutive tile indices walk down the rows first (CTAs running together share a
+// B panel); otherwise they walk across the columns first (CTAs share an A panel).
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int m_fastest,
+                                            int& m_tile, int& n_tile) {
+    if (m_fastest) {
+        m_tile = tile % m_tiles;
+        n_tile = tile / m_tiles;
+    } else {
+        n_tile = tile % n_tiles;
+        m_tile = tile / n_tiles;
+    }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               int m_tiles, int n_tiles, int k_blocks, int m_fastest,
+               const typename Epi::Params ep, int* __restrict__ status) {
+    using S = GemmSmem<BN, STAGES>;
+    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width");
+    static_assert(2 * BN <= 512, "two accumulator buffers must fit in tensor memory");
+    constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+    constexpr uint32_t kIdesc = ptx::make_idesc_f16(kBM, BN, IS_BF16, A_MN, B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + STAGES * S::kStageBytes;
+    // barrier block: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | drain | tmem ptr | abort
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+    uint8_t* gen_bar_base = smem_raw + (bar_base - ptx::smem_u32(smem_raw));
+    volatile uint32_t* tmem_ptr_smem =
+        reinterpret_cast<volatile uint32_t*>(gen_bar_base + 8 * (2 * STAGES + 5));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar_base + 8 * (2 * STAGES + 5) + 4);
+    static_assert(8 * (2 * STAGES + 6) <= S::kBarrierBytes, "barrier block too small");
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (ptx::elect_one()) {
+            uint32_t issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int m_tile, n_tile;
+                tile_coords(tile, m_tiles, n_tiles, m_fastest, m_tile, n_tile);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    const uint32_t stage = issued % STAGES;
+                    const uint32_t phase = (issued / STAGES) & 1u;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = smem_base + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kABytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+                    if constexpr (!A_MN) {
+                        ptx::tma_load_2d(sa, &tmA, full_bar(stage), kb * kBK, m_tile * kBM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kBM / 64; ++j)
+                            ptx::tma_load_2d(sa + j * (kBK * 128), &tmA, full_bar(stage),
+                                             m_tile * kBM + j * 64, kb * kBK);
+                    }
+                    if constexpr (!B_MN) {
+                        ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n_tile * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_2d(sb + j * (kBK * 128), &tmB, full_bar(stage),
+                                             n_tile * BN + j * 64, kb * kBK);
+                    }
+                    ++issued;
+                }
+            }
+            if (!ok || *abort_flag) {
+                // Unwinding: let every copy already in flight land before the CTA retires.
+                if (!ok) atomicCAS(status, 0, kDevErrProducerTimeout);
+                const uint32_t back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+                for (uint32_t j = 1; j <= back; ++j) {
+                    const uint32_t i = issued - j;
+                    const uint32_t bar = full_bar(i % STAGES);
+                    const uint32_t par = (i / STAGES) & 1u;
+                    for (int spin = 0; spin < (1 << 16); ++spin)
+                        if (ptx::mbar_try_wait(bar, par)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            uint32_t consumed = 0;
+            uint32_t local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const uint32_t buf = local_tile & 1u;
+                const uint32_t buf_phase = (local_tile >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty_bar(buf), buf_phase ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    const uint32_t stage = consumed % STAGES;
+                    const uint32_t phase = (consumed / STAGES) & 1u;
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa = smem_base + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // K-major: 16 elements = 32 bytes further along the swizzled row.
+                        // MN-major: 16 k-rows of 128 bytes further down.
+                        const uint64_t da =
+                            A_MN ? ptx::make_smem_desc(sa + k * (kUmmaK * 128), kBK * 128, 1024)
+                                 : ptx::make_smem_desc(sa + k * (kUmmaK * 2), 0, 1024);
+                        const uint64_t db =
+                            B_MN ? ptx::make_smem_desc(sb + k * (kUmmaK * 128), kBK * 128, 1024)
+                                 : ptx::make_smem_desc(sb + k * (kUmmaK * 2), 0, 1024);
+                        ptx::umma_f16(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(empty_bar(stage));  // smem slot reusable once these MMAs retire
+                    ++consumed;
+                }
+                if (ok) ptx::umma_commit(tfull_bar(buf));  // accumulator complete
+            }
+            if (!ok || *abort_flag) {
+                if (!ok) atomicCAS(status, 0, kDevErrMmaTimeout);
+                // Unwinding: wait (bounded) for the MMAs already issued before TMEM is freed.
+                ptx::umma_commit(drain_bar);
+                for (int spin = 0; spin < (1 << 16); ++spin)
+                    if (ptx::mbar_try_wait(drain_bar, 0)) break;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        uint32_t local_tile = 0;
+        bool ok = true;
+        typename Epi::State st;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+            int m_tile, n_tile;
+            tile_coords(tile, m_tiles, n_tiles, m_fastest, m_tile, n_tile);
+            const uint32_t buf = local_tile & 1u;
+            const uint32_t buf_phase = (local_tile >> 1) & 1u;
+            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN};
+            Epi::begin(st, ep, tc);  // global loads for this row overlap the wait below
+            if (!ptx::mbar_wait(tfull_bar(buf), buf_phase, abort_flag)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                ptx::tmem_ld_32x32(taddr + c * 32, v);
+                ptx::tmem_ld_wait();
+                Epi::chunk(st, ep, tc, c * 32, v);
+            }
+            // all TMEM reads of this buffer are done: hand it back before touching global memory
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            Epi::end(st, ep, tc);
+        }
+        if (!ok && lane == 0) atomicCAS(status, 0, kDevErrEpilogueTimeout);
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace lce

@@ -1,0 +1,558 @@
+// extern "C" entry points of libhelion_lce.so (declared in include/helion_lce.h): argument checks,
+// tensor-map construction, the block plan of the backward pass, and the kernel launches.
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <type_traits>
+
+#include "../../include/helion_lce.h"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "row_kernels.cuh"
+
+namespace lce {
+
+__device__ int g_device_status = 0;
+
+namespace {
+
+constexpr int kBN = 256;
+constexpr int kStages = 4;
+constexpr size_t kDefaultBlockBytes = 256ull << 20;
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status_ptr = nullptr;
+};
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_mutex;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+int device_info(DeviceInfo** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LCE_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return LCE_ERR_ARG;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if (!d.ready) {
+        if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return LCE_ERR_CUDA;
+        if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return LCE_ERR_CUDA;
+        if (d.cc_major == 10) {
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return LCE_ERR_CUDA;
+            d.status_ptr = static_cast<int*>(p);
+        }
+        d.ready = true;
+    }
+    if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || fn == nullptr)
+            return LCE_ERR_CUDA;
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    *out = &d;
+    return d.cc_major == 10 ? LCE_OK : LCE_ERR_ARCH;
+}
+
+inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
+inline size_t elem_size(int dtype) { return dtype == LCE_DTYPE_F32 ? 4 : 2; }
+
+// 2-D tensor map over a row-major 16-bit matrix: `inner` contiguous elements per row, `outer`
+// rows, `pitch_bytes` between rows; 128-byte swizzle; out-of-range elements read as zero.
+int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, long long outer,
+              long long pitch_bytes, unsigned box_inner, unsigned box_outer) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_bytes & 15) != 0) return LCE_ERR_ALIGN;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt =
+        dtype == LCE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? LCE_OK : LCE_ERR_CUDA;
+}
+
+// One operand of a GEMM as the host sees it: a row-major matrix [rows, cols] with a pitch.
+// As a K-major operand its rows are the m (n) index; as an MN-major operand its rows are k.
+struct Mat {
+    const void* ptr;
+    long long rows, cols, pitch_elems;
+};
+
+template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
+              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
+    const int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
+    CUtensorMap tma, tmb;
+    int rc;
+    if (A_MN) rc = make_tmap(&tma, a.ptr, dtype, M, K, a.pitch_elems * 2, 64, kBK);
+    else rc = make_tmap(&tma, a.ptr, dtype, K, M, a.pitch_elems * 2, kBK, kBM);
+    if (rc) return rc;
+    if (B_MN) rc = make_tmap(&tmb, b.ptr, dtype, Nn, K, b.pitch_elems * 2, 64, kBK);
+    else rc = make_tmap(&tmb, b.ptr, dtype, K, Nn, b.pitch_elems * 2, kBK, kBN);
+    if (rc) return rc;
+    const long long m_tiles = cdiv(M, kBM), n_tiles = cdiv(Nn, kBN), k_blocks = cdiv(K, kBK);
+    if (m_tiles * n_tiles > 0x7fffffffll || k_blocks > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
+    if (m_tiles * n_tiles == 0 || k_blocks == 0) return LCE_OK;
+    auto kern = gemm_tc_kernel<kBN, kStages, A_MN, B_MN, IS_BF16, Epi>;
+    constexpr int smem = GemmSmem<kBN, kStages>::kTotalBytes;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return LCE_ERR_CUDA;
+    const int grid = static_cast<int>(m_tiles * n_tiles < d.sm_count ? m_tiles * n_tiles : d.sm_count);
+    kern<<<grid, kGemmThreads, smem, stream>>>(tma, tmb, static_cast<int>(m_tiles),
+                                               static_cast<int>(n_tiles), static_cast<int>(k_blocks),
+                                               m_fastest, ep, d.status_ptr);
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+template <class T, class Epi>
+int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool b_mn, long long M,
+                long long Nn, long long K, const typename Epi::Params& ep, cudaStream_t stream) {
+    SimtOperand<T> A, B;
+    A.ptr = static_cast<const T*>(a.ptr);
+    A.stride_mn = a_mn ? 1 : a.pitch_elems;
+    A.stride_k = a_mn ? a.pitch_elems : 1;
+    A.extent_mn = static_cast<int>(M);
+    B.ptr = static_cast<const T*>(b.ptr);
+    B.stride_mn = b_mn ? 1 : b.pitch_elems;
+    B.stride_k = b_mn ? b.pitch_elems : 1;
+    B.extent_mn = static_cast<int>(Nn);
+    const long long m_tiles = cdiv(M, kBM), n_tiles = cdiv(Nn, kSimtBN);
+    if (m_tiles * n_tiles > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
+    if (m_tiles * n_tiles == 0 || K == 0) return LCE_OK;
+    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    const int grid = static_cast<int>(m_tiles * n_tiles < cap ? m_tiles * n_tiles : cap);
+    gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(
+        A, B, static_cast<int>(K), static_cast<int>(m_tiles), static_cast<int>(n_tiles), ep);
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The tcgen05 path needs 16-bit inputs, 16-byte aligned bases and row pitches (H % 8 == 0).
+int choose_path(int dtype, long long H, const void* x, const void* w, unsigned flags, bool* use_tc) {
+    const bool can_tc = dtype != LCE_DTYPE_F32 && (H % 8) == 0 && aligned16(x) && aligned16(w);
+    if (flags & LCE_FLAG_FORCE_TC) {
+        if (flags & LCE_FLAG_FORCE_SIMT) return LCE_ERR_ARG;
+        if (dtype == LCE_DTYPE_F32) return LCE_ERR_ARG;
+        if (!can_tc) return LCE_ERR_ALIGN;
+        *use_tc = true;
+        return LCE_OK;
+    }
+    *use_tc = can_tc && !(flags & LCE_FLAG_FORCE_SIMT);
+    return LCE_OK;
+}
+
+int check_dims(long long N, long long H, long long V, int dtype) {
+    if (N < 0 || H <= 0 || V <= 0) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if (N > 0x7fffff00ll || H > 0x7fffff00ll || V > 0x7fffff00ll) return LCE_ERR_TOO_LARGE;
+    return LCE_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+struct FwdLayout {
+    long long n_tiles, row_stride;
+    size_t bytes;
+};
+FwdLayout fwd_layout(long long N, long long V, bool use_tc) {
+    FwdLayout l;
+    l.n_tiles = cdiv(V, use_tc ? kBN : kSimtBN);
+    l.row_stride = static_cast<long long>(align_up(static_cast<size_t>(N), 64));
+    l.bytes = static_cast<size_t>(l.n_tiles) * 3 * l.row_stride * sizeof(float);
+    return l;
+}
+
+template <class T>
+int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const void* w, const void* tgt,
+                       int tgt_i64, long long N, long long H, long long V, long long vocab_start,
+                       float* stats, void* ws, cudaStream_t stream) {
+    const FwdLayout l = fwd_layout(N, V, use_tc);
+    EpiStats::Params ep;
+    ep.tgt = tgt;
+    ep.tgt_i64 = tgt_i64;
+    ep.rows = static_cast<int>(N);
+    ep.vocab = static_cast<int>(V);
+    ep.vocab_start = vocab_start;
+    ep.partial = static_cast<float*>(ws);
+    ep.row_stride = l.row_stride;
+    const Mat a{x, N, H, H}, b{w, V, H, H};
+    int rc;
+    if (use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+            rc = launch_tc<false, false, kBf16, EpiStats>(d, a, b, N, V, H, /*m_fastest=*/1, ep, stream);
+        } else {
+            rc = LCE_ERR_ARG;
+        }
+    } else {
+        rc = launch_simt<T, EpiStats>(d, a, false, b, false, N, V, H, ep, stream);
+    }
+    if (rc) return rc;
+    const int threads = 256;
+    merge_partials_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, stream>>>(
+        static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), stats);
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward block plan
+// ---------------------------------------------------------------------------------------------
+// G = dLoss/dLogits is produced one block [nr rows x nc vocab columns] at a time and consumed at
+// once by the dW and dX GEMMs. A block spanning all rows (vocab bands) completes dW[band] in one
+// launch and sums dX over bands; a block spanning the whole vocabulary (row chunks) completes
+// dX[chunk] and sums dW over chunks. The plan takes whichever moves fewer fp32 partial sums and
+// falls back to a 2-D grid of blocks when neither fits the byte cap.
+struct BwdPlan {
+    long long nr, nc;          // block shape (last blocks may be smaller)
+    long long n_rblk, n_cblk;  // number of row chunks / vocab bands
+    long long ldg;             // pitch of the G block in elements
+    long long bn;              // tile width of the dX / dW GEMMs (for the scratch layout)
+    size_t off_count, off_rowscale, off_g, off_dx_scratch, off_dw_scratch, total;
+    long long dw_band_scratch_floats;
+};
+
+BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use_tc, unsigned flags,
+                      size_t block_bytes) {
+    BwdPlan p{};
+    const size_t e = elem_size(dtype);
+    const size_t cap = block_bytes ? block_bytes : kDefaultBlockBytes;
+    const long long col_q = 256, row_q = 128;
+    const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
+    if (static_cast<size_t>(N) * V * e <= cap || N == 0) {
+        p.nr = N > 0 ? N : 1;
+        p.nc = V;
+    } else {
+        long long nc_band = static_cast<long long>(cap / (static_cast<size_t>(N) * e)) / col_q * col_q;
+        long long nr_chunk = static_cast<long long>(cap / (static_cast<size_t>(V) * e)) / row_q * row_q;
+        const bool band_ok = nc_band >= col_q, chunk_ok = nr_chunk >= row_q;
+        // fp32 partial-sum traffic (read + write) each choice causes
+        const double cost_band = band_ok ? (cdiv(V, nc_band) - 1) * 8.0 * N * H * (need_dx ? 1 : 0) : 1e300;
+        const double cost_chunk = chunk_ok ? (cdiv(N, nr_chunk) - 1) * 8.0 * V * H * (need_dw ? 1 : 0) : 1e300;
+        if (band_ok && cost_band <= cost_chunk) {
+            p.nr = N;
+            p.nc = nc_band;
+        } else if (chunk_ok) {
+            p.nr = nr_chunk;
+            p.nc = V;
+        } else {
+            p.nr = 8192 < N ? 8192 : N;
+            p.nc = static_cast<long long>(cap / (static_cast<size_t>(p.nr) * e)) / col_q * col_q;
+            if (p.nc < col_q) p.nc = col_q;
+            if (p.nc > V) p.nc = V;
+        }
+    }
+    p.n_rblk = N > 0 ? cdiv(N, p.nr) : 0;
+    p.n_cblk = cdiv(V, p.nc);
+    p.ldg = static_cast<long long>(align_up(static_cast<size_t>(p.nc), 256));
+    p.bn = use_tc ? kBN : kSimtBN;
+    size_t off = 0;
+    p.off_count = off;
+    off += 256;
+    p.off_rowscale = off;
+    off += align_up(static_cast<size_t>(N > 0 ? N : 1) * sizeof(float), 256);
+    p.off_g = off;
+    off += align_up(static_cast<size_t>(p.nr) * p.ldg * e, 256);
+    p.off_dx_scratch = off;
+    if (need_dx && p.n_cblk > 1)
+        off += align_up(static_cast<size_t>(cdiv(p.nr, kBM)) * cdiv(H, p.bn) * kBM * p.bn * sizeof(float), 256);
+    p.off_dw_scratch = off;
+    p.dw_band_scratch_floats = cdiv(p.nc, kBM) * cdiv(H, p.bn) * kBM * p.bn;
+    if (need_dw && p.n_rblk > 1)
+        off += align_up(static_cast<size_t>(p.n_cblk) * p.dw_band_scratch_floats * sizeof(float), 256);
+    p.total = off;
+    return p;
+}
+
+int store_mode(long long idx, long long count) {
+    if (count <= 1) return kStoreDirect;
+    if (idx == 0) return kStoreFirst;
+    return idx == count - 1 ? kStoreLast : kStoreAccum;
+}
+
+template <class T, class TDx>
+int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void* x, const void* w,
+                  const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
+                  long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, cudaStream_t stream) {
+    const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
+    const T* xp = static_cast<const T*>(x);
+    const T* wp = static_cast<const T*>(w);
+    T* g = reinterpret_cast<T*>(ws + p.off_g);
+    const float* rowscale = reinterpret_cast<const float*>(ws + p.off_rowscale);
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+
+    for (long long rb = 0; rb < p.n_rblk; ++rb) {
+        const long long r0 = rb * p.nr;
+        const long long nr = (N - r0 < p.nr) ? N - r0 : p.nr;
+        for (long long cb = 0; cb < p.n_cblk; ++cb) {
+            const long long c0 = cb * p.nc;
+            const long long nc = (V - c0 < p.nc) ? V - c0 : p.nc;
+            int rc;
+            // ---- step 1: G block = (softmax - onehot) * rowscale, from recomputed logits
+            {
+                typename EpiGrad<T>::Params ep;
+                ep.tgt = tgt;
+                ep.tgt_i64 = tgt_i64;
+                ep.rows = static_cast<int>(nr);
+                ep.cols = static_cast<int>(nc);
+                ep.row_off = static_cast<int>(r0);
+                ep.col_global0 = vocab_start + c0;
+                ep.lse = lse;
+                ep.rowscale = rowscale;
+                ep.g = g;
+                ep.ldg = p.ldg;
+                const Mat a{xp + r0 * H, nr, H, H}, b{wp + c0 * H, nc, H, H};
+                if (use_tc) {
+                    if constexpr (sizeof(T) == 2)
+                        rc = launch_tc<false, false, kBf16, EpiGrad<T>>(d, a, b, nr, nc, H, 1, ep, stream);
+                    else rc = LCE_ERR_ARG;
+                } else {
+                    rc = launch_simt<T, EpiGrad<T>>(d, a, false, b, false, nr, nc, H, ep, stream);
+                }
+                if (rc) return rc;
+            }
+            const Mat gm{g, nr, nc, p.ldg};
+            // ---- step 2: dW[c0 : c0+nc, :] (+)= G^T @ X[r0 : r0+nr, :]
+            if (need_dw) {
+                typename EpiStore<T>::Params ep;
+                ep.out = static_cast<T*>(dw) + c0 * H;
+                ep.ldo = H;
+                ep.rows = static_cast<int>(nc);
+                ep.cols = static_cast<int>(H);
+                ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
+                ep.mode = store_mode(rb, p.n_rblk);
+                const Mat b{xp + r0 * H, nr, H, H};
+                if (use_tc) {
+                    if constexpr (sizeof(T) == 2)
+                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream);
+                    else rc = LCE_ERR_ARG;
+                } else {
+                    rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream);
+                }
+                if (rc) return rc;
+            }
+            // ---- step 3: dX[r0 : r0+nr, :] (+)= G @ W[c0 : c0+nc, :]
+            if (need_dx) {
+                typename EpiStore<TDx>::Params ep;
+                ep.out = static_cast<TDx*>(dx) + r0 * H;
+                ep.ldo = H;
+                ep.rows = static_cast<int>(nr);
+                ep.cols = static_cast<int>(H);
+                ep.scratch = reinterpret_cast<float*>(ws + p.off_dx_scratch);
+                ep.mode = store_mode(cb, p.n_cblk);
+                const Mat b{wp + c0 * H, nc, H, H};
+                if (use_tc) {
+                    if constexpr (sizeof(T) == 2)
+                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, gm, b, nr, H, nc, 0, ep, stream);
+                    else rc = LCE_ERR_ARG;
+                } else {
+                    rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream);
+                }
+                if (rc) return rc;
+            }
+        }
+    }
+    return LCE_OK;
+}
+
+}  // namespace
+}  // namespace lce
+
+using namespace lce;
+
+extern "C" {
+
+int lce_version(void) { return LCE_VERSION; }
+
+const char* lce_strerror(int code) {
+    switch (code) {
+        case LCE_OK: return "ok";
+        case LCE_ERR_ARG: return "invalid argument (null pointer, bad size or unknown enum)";
+        case LCE_ERR_ALIGN: return "tcgen05 path needs 16-byte aligned pointers and hidden_size % 8 == 0";
+        case LCE_ERR_WS_TOO_SMALL: return "workspace too small";
+        case LCE_ERR_ARCH: return "device is not compute capability 10.x (sm_100a only, no fallback)";
+        case LCE_ERR_CUDA: return "CUDA runtime or driver call failed";
+        case LCE_ERR_TOO_LARGE: return "dimension too large for 32-bit tile indexing";
+        default: return "unknown error";
+    }
+}
+
+int lce_device_status(int* status_out, int clear) {
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    if (cudaDeviceSynchronize() != cudaSuccess) return LCE_ERR_CUDA;
+    int v = 0;
+    if (cudaMemcpy(&v, d->status_ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return LCE_ERR_CUDA;
+    if (clear && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpy(d->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    if (status_out) *status_out = v;
+    return LCE_OK;
+}
+
+size_t lce_forward_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags) {
+    if (check_dims(N, H, V, dtype)) return 0;
+    // size for the finer (SIMT) tiling unless the caller pins the tcgen05 path
+    const bool tc_only = (flags & LCE_FLAG_FORCE_TC) != 0;
+    return align_up(fwd_layout(N, V, tc_only).bytes, 256) + 256;
+}
+
+int lce_forward_stats(const void* x, const void* w, const void* target, int target_is_i64, int64_t N,
+                      int64_t H, int64_t V, int64_t vocab_start, int dtype, float* stats, void* ws,
+                      size_t ws_bytes, unsigned flags, void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (N == 0) return LCE_OK;
+    if (!x || !w || !target || !stats || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    if (ws_bytes < fwd_layout(N, V, use_tc).bytes) return LCE_ERR_WS_TOO_SMALL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+        case LCE_DTYPE_F16:
+            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+        default:
+            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+    }
+}
+
+size_t lce_finalize_workspace_bytes(int64_t N) {
+    return align_up(static_cast<size_t>(N > 0 ? N : 1) * sizeof(float), 256);
+}
+
+int lce_finalize(const float* stats, int R, const void* target, int target_is_i64, int64_t N,
+                 int64_t ignore_index, int reduction, float* lse, float* loss, float* valid_count,
+                 void* ws, size_t ws_bytes, void* stream) {
+    if (N < 0 || R < 1 || N > 0x7fffff00ll) return LCE_ERR_ARG;
+    if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
+        return LCE_ERR_ARG;
+    if (!loss) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* loss_rows = reduction == LCE_REDUCTION_NONE ? loss : static_cast<float*>(ws);
+    if (N > 0) {
+        if (!stats || !target || !lse) return LCE_ERR_ARG;
+        if (reduction != LCE_REDUCTION_NONE && (!ws || ws_bytes < static_cast<size_t>(N) * sizeof(float)))
+            return LCE_ERR_WS_TOO_SMALL;
+        const int threads = 256;
+        finalize_rows_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, s>>>(
+            stats, R, target, target_is_i64, static_cast<int>(N), ignore_index, lse, loss_rows);
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    if (reduction != LCE_REDUCTION_NONE || valid_count) {
+        reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
+                                              reduction == LCE_REDUCTION_MEAN ? 1 : 0,
+                                              reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    return LCE_OK;
+}
+
+size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags,
+                                    size_t block_bytes) {
+    if (check_dims(N, H, V, dtype)) return 0;
+    // the SIMT and tcgen05 plans differ only in scratch tiling; report the larger of the two
+    const size_t a = plan_backward(N, H, V, dtype, true, flags, block_bytes).total;
+    const size_t b = plan_backward(N, H, V, dtype, false, flags, block_bytes).total;
+    return a > b ? a : b;
+}
+
+int lce_backward(const void* x, const void* w, const void* target, int target_is_i64, const float* lse,
+                 const float* grad_out, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
+                 int64_t ignore_index, int reduction, void* dx, void* dw, void* ws, size_t ws_bytes,
+                 unsigned flags, size_t block_bytes, void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
+        return LCE_ERR_ARG;
+    const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
+    if ((need_dx && !dx && N > 0) || (need_dw && !dw)) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0) {
+        // no rows: dW is all zeros (tritium/ops/cross_entropy.py:912-913), dX is empty
+        if (need_dw && cudaMemsetAsync(dw, 0, static_cast<size_t>(V) * H * elem_size(dtype), s) != cudaSuccess)
+            return LCE_ERR_CUDA;
+        return LCE_OK;
+    }
+    if (!x || !w || !target || !lse || !grad_out || !ws) return LCE_ERR_ARG;
+    if (!need_dx && !need_dw) return LCE_OK;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    const BwdPlan p = plan_backward(N, H, V, dtype, use_tc, flags, block_bytes);
+    if (ws_bytes < p.total) return LCE_ERR_WS_TOO_SMALL;
+    char* wsc = static_cast<char*>(ws);
+    float* count = reinterpret_cast<float*>(wsc + p.off_count);
+    float* rowscale = reinterpret_cast<float*>(wsc + p.off_rowscale);
+    if (reduction == LCE_REDUCTION_MEAN) {
+        count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
+        target, target_is_i64, static_cast<int>(N), ignore_index, grad_out,
+        reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0, count, rowscale);
+    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
+#define LCE_BWD(T)                                                                                          \
+    (dx32 ? backward_impl<T, float>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
+                                    dx, dw, wsc, flags, s)                                                  \
+          : backward_impl<T, T>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
+                                dw, wsc, flags, s))
+    switch (dtype) {
+        case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
+        case LCE_DTYPE_F16: return LCE_BWD(__half);
+        default: return LCE_BWD(float);
+    }
+#undef LCE_BWD
+}
+
+int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,
+                   int a_mn, int b_mn, int dtype, void* stream) {
+    if (!a || !b || !out || M <= 0 || N <= 0 || K <= 0) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EpiStore<float>::Params ep;
+    ep.out = out;
+    ep.ldo = N;
+    ep.rows = static_cast<int>(M);
+    ep.cols = static_cast<int>(N);
+    ep.scratch = nullptr;
+    ep.mode = kStoreDirect;
+    const Mat am = a_mn ? Mat{a, K, M, M} : Mat{a, M, K, K};
+    const Mat bm = b_mn ? Mat{b, K, N, N} : Mat{b, N, K, K};
+#define LCE_DBG(AMN, BMN)                                                                               \
+    (dtype == LCE_DTYPE_BF16 ? launch_tc<AMN, BMN, true, EpiStore<float>>(*d, am, bm, M, N, K, 1, ep, s) \
+                             : launch_tc<AMN, BMN, false, EpiStore<float>>(*d, am, bm, M, N, K, 1, ep, s))
+    if (!a_mn && !b_mn) return LCE_DBG(false, false);
+    if (!a_mn && b_mn) return LCE_DBG(false, true);
+    if (a_mn && !b_mn) return LCE_DBG(true, false);
+    return LCE_DBG(true, true);
+#undef LCE_DBG
+}
+
+}  // extern "C"

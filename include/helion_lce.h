@@ -1,0 +1,122 @@
+/* C ABI of the B200 (sm_100a) fused linear-cross-entropy library (libhelion_lce.so).
+ *
+ * The library replaces the GPU work behind two public functions of the reference,
+ *   tritium.linear_cross_entropy           (tritium/ops/cross_entropy.py:716-725)
+ *   tritium.linear_cross_entropy_backward  (tritium/ops/cross_entropy.py:863-959)
+ * i.e. loss = cross_entropy(hidden @ weight^T, target) and its gradients, without ever writing the
+ * N x V logits to memory. The reference has no FFI of its own (it launches Triton kernels from
+ * Python); each entry point below names the reference host function whose launches it replaces.
+ *
+ * Conventions
+ *   - every pointer is a device pointer owned by the caller unless stated otherwise; the library
+ *     allocates nothing and keeps no reference after the call returns;
+ *   - a call only enqueues work on `stream` (a cudaStream_t passed as void*) of the current
+ *     device and returns; it never synchronises;
+ *   - return value 0 = enqueued; anything else is a synchronous argument / launch error, see
+ *     lce_strerror(). There is no CPU fallback: a device that is not sm_100 yields LCE_ERR_ARCH;
+ *   - x is [N, H] row-major, w is [V_local, H] row-major (rows vocab_start .. vocab_start+V_local
+ *     of the full weight when the vocabulary is sharded), targets are GLOBAL vocabulary indices;
+ *   - `ws` is scratch memory of at least the matching *_workspace_bytes(); its contents are
+ *     undefined before and after a call, and calls that overlap in time need distinct scratch.
+ */
+#ifndef HELION_LCE_H_
+#define HELION_LCE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LCE_VERSION 1
+
+/* element type of x, w, dx, dw */
+#define LCE_DTYPE_BF16 0
+#define LCE_DTYPE_F16 1
+#define LCE_DTYPE_F32 2
+
+/* loss reduction (torch.nn.functional.cross_entropy semantics) */
+#define LCE_REDUCTION_NONE 0
+#define LCE_REDUCTION_MEAN 1
+#define LCE_REDUCTION_SUM 2
+
+/* flags */
+#define LCE_FLAG_FORCE_SIMT 1u /* CUDA-core kernels even where the tcgen05 path applies        */
+#define LCE_FLAG_FORCE_TC 2u   /* tcgen05 kernels or LCE_ERR_ARG; never a silent switch         */
+#define LCE_FLAG_DX_F32 4u     /* dx is float32 [N, H]: a partial sum another rank will reduce   */
+#define LCE_FLAG_NO_DX 8u      /* skip dX (dx may be NULL)                                       */
+#define LCE_FLAG_NO_DW 16u     /* skip dW (dw may be NULL)                                       */
+
+/* status codes */
+#define LCE_OK 0
+#define LCE_ERR_ARG 1          /* NULL pointer, negative size, unknown enum                      */
+#define LCE_ERR_ALIGN 2        /* tcgen05 path forced but a pointer / pitch is not 16-byte aligned */
+#define LCE_ERR_WS_TOO_SMALL 3
+#define LCE_ERR_ARCH 4         /* current device is not compute capability 10.x                  */
+#define LCE_ERR_CUDA 5         /* a CUDA runtime / driver call failed                            */
+#define LCE_ERR_TOO_LARGE 6    /* a dimension exceeds what 32-bit tile indexing supports         */
+
+int lce_version(void);
+const char* lce_strerror(int code);
+
+/* Reads (and optionally clears) the per-device status word that kernels set when one of their
+ * bounded waits ran out (0 = no such event). Synchronises the device; meant for tests. */
+int lce_device_status(int* status_out, int clear);
+
+/* ---- forward ---------------------------------------------------------------------------------
+ * Replaces the launches of _linear_cross_entropy_forward (tritium/ops/cross_entropy.py:563-640):
+ * the partial-forward kernel (:192-248) or the direct kernel (:134-189).
+ * Writes per-row softmax statistics of the LOCAL vocabulary shard, component-major:
+ *   stats[0*N + i] = max_j z[i,j]   stats[1*N + i] = sum_j exp(z[i,j] - max)
+ *   stats[2*N + i] = z[i, target_i] if vocab_start <= target_i < vocab_start + V_local else -inf
+ */
+size_t lce_forward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags);
+int lce_forward_stats(const void* x, const void* w, const void* target, int target_is_i64,
+                      int64_t N, int64_t H, int64_t V_local, int64_t vocab_start, int dtype,
+                      float* stats, void* ws, size_t ws_bytes, unsigned flags, void* stream);
+
+/* Replaces _linear_cross_entropy_reduce_forward_kernel (tritium/ops/cross_entropy.py:251-293):
+ * merges the statistics of R shards (stats is [R][3][N], shard r at stats + r*3*N; R = 1 on one
+ * GPU) in shard order and produces
+ *   lse[i]  = logsumexp over the full vocabulary (fp32 [N], also for ignored rows)
+ *   loss    = one float for MEAN / SUM, N floats for NONE (0 for ignored rows)
+ *   valid_count (optional, may be NULL) = number of rows with target != ignore_index, as float
+ * The sum over rows uses a fixed tree, so the loss is bit-identical from run to run (the
+ * reference accumulates with atomics). ws: lce_finalize_workspace_bytes(N). */
+size_t lce_finalize_workspace_bytes(int64_t N);
+int lce_finalize(const float* stats, int R, const void* target, int target_is_i64, int64_t N,
+                 int64_t ignore_index, int reduction, float* lse, float* loss, float* valid_count,
+                 void* ws, size_t ws_bytes, void* stream);
+
+/* ---- backward --------------------------------------------------------------------------------
+ * Replaces linear_cross_entropy_backward (tritium/ops/cross_entropy.py:863-959): the fused
+ * small-shape kernel (:296-382) and the chunk loop of F.linear / in-place softmax-gradient /
+ * mm / addmm (:927-957).
+ *   G  = (softmax(z) - onehot(target)) * scale_i, rounded to the input dtype
+ *        scale_i = grad_out / valid_count (MEAN), grad_out (SUM), grad_out[i] (NONE); 0 if ignored
+ *   dx = G  @ w   [N, H]        (input dtype, or float32 partial with LCE_FLAG_DX_F32)
+ *   dw = G^T @ x  [V_local, H]  (input dtype)
+ * grad_out is read on the device: one float for MEAN / SUM, N floats for NONE.
+ * G is staged block by block through `ws` (block_bytes caps one block; 0 = default 256 MiB), and
+ * partial sums over blocks are added in a fixed order in fp32, so results are deterministic. */
+size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
+                                    size_t block_bytes);
+int lce_backward(const void* x, const void* w, const void* target, int target_is_i64,
+                 const float* lse, const float* grad_out, int64_t N, int64_t H, int64_t V_local,
+                 int64_t vocab_start, int dtype, int64_t ignore_index, int reduction, void* dx,
+                 void* dw, void* ws, size_t ws_bytes, unsigned flags, size_t block_bytes,
+                 void* stream);
+
+/* ---- test hook -------------------------------------------------------------------------------
+ * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
+ * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b
+ * with N. No counterpart in the reference; exists so the operand-layout handling can be tested
+ * in isolation. */
+int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,
+                   int a_mn_major, int b_mn_major, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELION_LCE_H_ */

@@ -1,0 +1,223 @@
+"""CPU oracle for the fused linear-cross-entropy path. TEST INFRASTRUCTURE ONLY.
+
+Nothing in the product imports this module: only tests/, __graft_entry__.smoke() and the CPU-baseline
+legs of bench.py may call it, and only as the checker or the timed CPU baseline. The product path
+(helion_b200) has no CPU route and fails loudly without its CUDA library.
+
+Two layers:
+
+1. ``expression`` / ``expression_chunked`` - the ground truth the reference itself tests and benchmarks
+   against: ``F.cross_entropy(F.linear(hidden, weight).float(), target)`` evaluated in fp32 on inputs that
+   were first rounded to the working dtype (reference ``tests/tritium/test_cross_entropy.py:72, 91-93,
+   106-108``; ``benchmarks/bench_linear_cross_entropy.py:34-39``). The reference has no CPU
+   implementation of the op (CPU tensors are rejected, ``tritium/ops/_utils.py:25-27``), so this
+   expression is also the reference's CPU path for timing purposes.
+2. ``restated_forward`` / ``restated_backward`` - a plain restatement of the algorithm the reference's
+   kernels run (block-partial softmax statistics merged per row; chunked recompute backward), following
+   ``tritium/ops/cross_entropy.py`` line by line, including where it rounds to the input dtype.
+
+Pinning: the reference ships no golden vectors for this path. The restatement is pinned against outputs
+of the reference's own Triton kernels, produced on a B200 by tests/golden/make_golden.py and committed
+under tests/golden/ (forward and the small-shape fused backward). The reference's large-shape backward
+(cuBLAS chunk loop, ``cross_entropy.py:927-957``) has no test in the reference; fixtures from a run of
+it are committed as well, and where none exists for a shape that branch is "parity unpinned" and
+``expression`` stands in.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+REFERENCE_BLOCK_V = 128              # LINEAR_CE_BLOCK_V, tritium/ops/cross_entropy.py:24
+REFERENCE_DIRECT_MAX_VOCAB = 256     # LINEAR_CE_DIRECT_MAX_VOCAB, :25
+REFERENCE_MAX_LOGIT_ELEMENTS = 67_108_864  # LINEAR_CE_BACKWARD_MAX_LOGIT_ELEMENTS, :22
+
+
+# ----------------------------------------------------------------------------------------------
+# 1. the ground-truth expression
+# ----------------------------------------------------------------------------------------------
+def expression(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, *, reduction: str = "mean",
+               ignore_index: int = -100, grad_out: torch.Tensor | None = None, want_grads: bool = True) -> dict:
+    """fp32 ``F.cross_entropy(F.linear(h, w), t)`` and its autograd gradients (tests :88-95)."""
+    h32 = hidden.detach().float().reshape(-1, hidden.shape[-1]).clone().requires_grad_(want_grads)
+    w32 = weight.detach().float().clone().requires_grad_(want_grads)
+    t = target.reshape(-1).long()
+    logits = F.linear(h32, w32)
+    loss = F.cross_entropy(logits, t, ignore_index=ignore_index, reduction=reduction)
+    out = {"loss": loss.detach().reshape(target.shape if reduction == "none" else ()),
+           "lse": torch.logsumexp(logits.detach(), dim=-1)}
+    if want_grads:
+        if grad_out is None:
+            grad_out = torch.ones_like(loss)
+        loss.backward(grad_out.detach().float().reshape(loss.shape))
+        out["dx"] = h32.grad
+        out["dw"] = w32.grad
+    return out
+
+
+def expression_chunked(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, *,
+                       reduction: str = "mean", ignore_index: int = -100, grad_out: torch.Tensor | None = None,
+                       want_grads: bool = True, chunk_rows: int = 1024) -> dict:
+    """Same numbers as ``expression`` with O(chunk_rows x V) memory (for shapes whose logits do not fit)."""
+    h32 = hidden.detach().float().reshape(-1, hidden.shape[-1])
+    w32 = weight.detach().float()
+    t = target.reshape(-1).long()
+    n = h32.shape[0]
+    valid = t != ignore_index
+    count = valid.sum().to(torch.float32)
+    lse = torch.empty(n, dtype=torch.float32, device=h32.device)
+    nll = torch.zeros(n, dtype=torch.float32, device=h32.device)
+    if grad_out is None:
+        grad_out = torch.ones(n if reduction == "none" else (), dtype=torch.float32, device=h32.device)
+    go = grad_out.detach().float().to(h32.device)
+    if reduction == "none":
+        scale = go.reshape(-1)
+    elif reduction == "sum":
+        scale = go.expand(n)
+    else:
+        scale = (go / count).expand(n)
+    scale = torch.where(valid, scale, torch.zeros_like(scale))
+    dx = torch.empty_like(h32) if want_grads else None
+    dw = torch.zeros_like(w32) if want_grads else None
+    for r0 in range(0, n, chunk_rows):
+        r1 = min(n, r0 + chunk_rows)
+        z = h32[r0:r1] @ w32.T
+        l = torch.logsumexp(z, dim=-1)
+        lse[r0:r1] = l
+        tc = t[r0:r1]
+        vc = valid[r0:r1]
+        safe = torch.where(vc, tc, torch.zeros_like(tc))
+        nll[r0:r1] = torch.where(vc, l - z.gather(1, safe[:, None])[:, 0], torch.zeros_like(l))
+        if want_grads:
+            g = torch.exp(z - l[:, None])
+            g[torch.arange(r1 - r0, device=g.device)[vc], safe[vc]] -= 1.0
+            g *= scale[r0:r1, None]
+            dx[r0:r1] = g @ w32
+            dw += g.T @ h32[r0:r1]
+    if reduction == "none":
+        loss = nll.reshape(target.shape)
+    elif reduction == "sum":
+        loss = nll.sum()
+    else:
+        loss = nll.sum() / count
+    out = {"loss": loss, "lse": lse}
+    if want_grads:
+        out["dx"], out["dw"] = dx, dw
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# 2. restatement of the reference's algorithm
+# ----------------------------------------------------------------------------------------------
+def restated_forward(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor) -> dict:
+    """What the reference's forward kernels compute (tritium/ops/cross_entropy.py:563-640).
+
+    Logits are accumulated in fp32 from the working-dtype inputs (:220-233). For V <= 256 one block
+    holds the whole row (:134-189); otherwise each 128-wide vocab block yields (max, sum exp(z - max),
+    target logit or -inf) (:235-248) and a second pass merges the blocks per row (:251-293). The loss is
+    the mean over ALL rows (divisor n_rows, :189, :293); there is no ignored label, so a target no
+    column matches leaves target_logit = -inf and an infinite loss.
+    """
+    h32 = hidden.detach().float().reshape(-1, hidden.shape[-1])
+    w32 = weight.detach().float()
+    t = target.reshape(-1).long()
+    n, v = h32.shape[0], w32.shape[0]
+    z = h32 @ w32.T
+    cols = torch.arange(v)
+    if v <= REFERENCE_DIRECT_MAX_VOCAB:
+        row_max = z.max(dim=1).values
+        lse = torch.log(torch.exp(z - row_max[:, None]).sum(dim=1)) + row_max
+        tlogit = torch.where(cols[None, :] == t[:, None], z, torch.full_like(z, -math.inf)).max(dim=1).values
+    else:
+        pm, ps, pt = [], [], []
+        for b0 in range(0, v, REFERENCE_BLOCK_V):
+            zb = z[:, b0:b0 + REFERENCE_BLOCK_V]
+            bm = zb.max(dim=1).values
+            pm.append(bm)
+            ps.append(torch.exp(zb - bm[:, None]).sum(dim=1))
+            hit = cols[None, b0:b0 + REFERENCE_BLOCK_V] == t[:, None]
+            pt.append(torch.where(hit, zb, torch.full_like(zb, -math.inf)).max(dim=1).values)
+        pm, ps, pt = torch.stack(pm), torch.stack(ps), torch.stack(pt)
+        row_max = pm.max(dim=0).values
+        lse = torch.log((ps * torch.exp(pm - row_max[None, :])).sum(dim=0)) + row_max
+        tlogit = pt.max(dim=0).values
+    nll = lse - tlogit
+    return {"loss": nll.sum() / n if n != 1 else nll.sum(), "lse": lse}
+
+
+def restated_backward(grad_out: torch.Tensor, hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor,
+                      lse: torch.Tensor) -> dict:
+    """What linear_cross_entropy_backward computes (tritium/ops/cross_entropy.py:863-959).
+
+    Small shapes (H <= 64, V >= 256, N*V <= 65536; :522-531) run the fused kernel: fp32 logits,
+    G = (exp(z - lse) - onehot) * grad_out / n_rows rounded to the input dtype, dX and dW summed in fp32
+    and rounded once (:335-381, :860). Larger shapes run a row-chunk loop (:927-957): logits rounded to
+    the input dtype by F.linear (:937), G formed from those rounded logits and stored in the input dtype
+    (:103-131), dX = G @ W per chunk (:945), dW accumulated across chunks in the weight dtype (:947-957).
+    """
+    dt = hidden.dtype
+    h = hidden.detach().reshape(-1, hidden.shape[-1])
+    w = weight.detach()
+    t = target.reshape(-1).long()
+    n, hsz = h.shape
+    v = w.shape[0]
+    go = grad_out.detach().float().reshape(())
+    rows = torch.arange(n)
+    if hsz <= 64 and v >= 256 and n * v <= 65_536:
+        z = h.float() @ w.float().T
+        g = torch.exp(z - lse[:, None])
+        g[rows, t] -= 1.0
+        g = (g * (go / n)).to(dt).float()
+        return {"dx": (g @ w.float()).to(dt), "dw": (g.T @ h.float()).to(dt)}
+    chunk = min(n, max(1, REFERENCE_MAX_LOGIT_ELEMENTS // v))
+    dx = torch.empty_like(h)
+    dw = torch.zeros_like(w)
+    first = True
+    for r0 in range(0, n, chunk):
+        r1 = min(n, r0 + chunk)
+        z = (h[r0:r1].float() @ w.float().T).to(dt).float()
+        g = torch.exp(z - lse[r0:r1, None])
+        g[torch.arange(r1 - r0), t[r0:r1]] -= 1.0
+        g = (g * (go / n)).to(dt).float()
+        dx[r0:r1] = (g @ w.float()).to(dt)
+        part = g.T @ h[r0:r1].float()
+        dw = part.to(dt) if first else (dw.float() + part).to(dt)
+        first = False
+    return {"dx": dx, "dw": dw}
+
+
+# ----------------------------------------------------------------------------------------------
+# vocabulary sharding algebra (what each rank contributes and how the merge must come out)
+# ----------------------------------------------------------------------------------------------
+def shard_stats(hidden: torch.Tensor, weight_shard: torch.Tensor, target: torch.Tensor, vocab_start: int) -> torch.Tensor:
+    """``[3, N]`` fp32: (max, sum exp(z - max), target logit or -inf) over one contiguous vocab shard."""
+    h32 = hidden.detach().float().reshape(-1, hidden.shape[-1])
+    z = h32 @ weight_shard.detach().float().T
+    t = target.reshape(-1).long() - vocab_start
+    m = z.max(dim=1).values
+    s = torch.exp(z - m[:, None]).sum(dim=1)
+    inside = (t >= 0) & (t < z.shape[1])
+    safe = torch.where(inside, t, torch.zeros_like(t))
+    tl = torch.where(inside, z.gather(1, safe[:, None])[:, 0], torch.full_like(m, -math.inf))
+    return torch.stack([m, s, tl])
+
+
+def merge_stats(stats: torch.Tensor, target: torch.Tensor, *, reduction: str = "mean", ignore_index: int = -100) -> dict:
+    """Merge ``[R, 3, N]`` shard statistics into the global loss and logsumexp."""
+    m = stats[:, 0].max(dim=0).values
+    s = (stats[:, 1] * torch.exp(stats[:, 0] - m[None, :])).sum(dim=0)
+    lse = m + torch.log(s)
+    tl = stats[:, 2].max(dim=0).values
+    t = target.reshape(-1)
+    valid = t != ignore_index
+    nll = torch.where(valid, lse - tl, torch.zeros_like(lse))
+    if reduction == "none":
+        loss = nll.reshape(target.shape)
+    elif reduction == "sum":
+        loss = nll.sum()
+    else:
+        loss = nll.sum() / valid.sum()
+    return {"loss": loss, "lse": lse}
