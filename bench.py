@@ -1,0 +1,358 @@
+#!/usr/bin/env python
+"""Headline benchmark: fused linear-cross-entropy forward+backward on the Llama-3-8B LM head.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one forward + backward of the loss over one batch of synthetic tokens. At N GPUs the weight
+is sharded by vocabulary (one process per GPU, launched by torch.distributed.run) and the same batch is
+processed by all ranks together, so total work is fixed ("strong" scaling). Rank 0 prints ONE JSON line.
+
+``--impl reference`` times the reference's ground-truth expression (fp32 F.linear + F.cross_entropy +
+autograd, the expression the reference's tests and benchmark compare against) on the host CPU, on a
+bounded row sample of the same workload. The reference has no CPU implementation of its own and its GPU
+kernels are not the CPU baseline.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+METRIC = "linear_ce_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return {"burst": d["bf16_tflops"], "sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if world != n_gpus:
+            raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}")
+        return rank, world, local, dist
+    if n_gpus != 1:
+        raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    torch.cuda.set_device(0)
+    return 0, 1, 0, None
+
+
+def build_workload(name: str):
+    from helion_b200 import inputs
+
+    if name.startswith("sweep-"):
+        return inputs.sweep_config(int(name.split("-", 1)[1]))
+    return inputs.CONFIGS[name]
+
+
+def cpu_baseline(data: dict, sample_rows: int, repeats: int, warmup: int) -> dict:
+    """fp32 ground-truth expression on the host cores over the first `sample_rows` rows x full vocab."""
+    from oracle import oracle
+
+    h = data["hidden"].reshape(-1, data["hidden"].shape[-1])[:sample_rows]
+    t = data["target"].reshape(-1)[:sample_rows]
+    red = data["reduction"]
+    go = data["grad_out"]
+    times = []
+    for i in range(warmup + repeats):
+        t0 = time.perf_counter()
+        oracle.expression(h, data["weight"], t, reduction=red, ignore_index=data["ignore_index"], grad_out=go)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = statistics.median(times)
+    return {
+        "value": sample_rows / sec,
+        "unit": UNIT,
+        "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(),
+        "kind": "port",
+        "sample": f"first {sample_rows} rows x full vocab, fp32 F.linear+F.cross_entropy+autograd, "
+                  f"median of {repeats} after {warmup} warm-up, {sec:.3f} s each",
+        "seconds_per_sample": sec,
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from helion_b200 import inputs
+
+    cfg = build_workload(args.workload)
+    data = inputs.make_inputs(cfg)
+    flops_per_row = 8.0 * cfg.hidden * cfg.vocab
+    # about 2e12 FLOP of CPU work per step keeps a default run within a few minutes
+    sample_rows = max(16, min(cfg.rows, int(2.0e12 / flops_per_row)))
+    base = cpu_baseline(data, sample_rows, repeats=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+    sec = base["seconds_per_sample"]
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens": cfg.rows, "hidden": cfg.hidden, "vocab": cfg.vocab,
+                   "reduction": cfg.reduction, "sample_rows": sample_rows},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "host_cpus", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    from helion_b200 import _lib, inputs, ops
+
+    rank, world, local, dist = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    cfg = build_workload(args.workload)
+    data = inputs.make_inputs(cfg)
+    n, h, v = cfg.rows, cfg.hidden, cfg.vocab
+    if v % world:
+        raise SystemExit(f"vocab {v} is not divisible by {world} ranks")
+    v_loc = v // world
+    group = dist.group.WORLD if world > 1 else None
+
+    x_host = data["hidden"].pin_memory()
+    t_host = data["target"].pin_memory()
+    w = data["weight"][rank * v_loc:(rank + 1) * v_loc].to(dev).requires_grad_(True)
+    x = x_host.to(dev).requires_grad_(True)
+    t = t_host.to(dev)
+    go = data["grad_out"].to(dev)
+    red, ign = cfg.reduction, data["ignore_index"]
+    L = _lib.lib()
+
+    def step(xx, tt):
+        xx.grad = None
+        w.grad = None
+        loss = ops.linear_cross_entropy(xx, w, tt, reduction=red, ignore_index=ign, process_group=group)
+        loss.backward(go)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        tt = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        loss = step(x, t)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.lce_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(x, t)
+    e1.record()
+    barrier()
+    launches = L.lce_launch_count() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    loss_value = float(loss.item())
+
+    # ---- end to end: this step's activations and labels come from pinned host memory, the loss goes back
+    x2 = torch.empty_like(x).requires_grad_(True)
+    t2 = torch.empty_like(t)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def step_e2e():
+        with torch.no_grad():
+            x2.copy_(x_host, non_blocking=True)
+            t2.copy_(t_host, non_blocking=True)
+        l2 = step(x2, t2)
+        loss_host.copy_(l2.detach(), non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e3.record()
+    barrier()
+    ms_e2e = max_over_ranks(e2.elapsed_time(e3)) / args.steps
+
+    # ---- dominant kernel, timed alone through the C ABI: the forward logits GEMM + statistics
+    stats = torch.empty((3, n), dtype=torch.float32, device=dev)
+    ws = torch.empty(L.lce_forward_workspace_bytes(n, h, v_loc, _lib.DTYPE_BF16, 0), dtype=torch.uint8, device=dev)
+    x2d = x.detach().view(n, h)
+    t1d = t.view(n)
+
+    def fwd_kernel():
+        _lib.check(L.lce_forward_stats(x2d.data_ptr(), w.data_ptr(), t1d.data_ptr(), 1, n, h, v_loc, rank * v_loc,
+                                       _lib.DTYPE_BF16, stats.data_ptr(), ws.data_ptr(), ws.numel(), 0,
+                                       torch.cuda.current_stream().cuda_stream), "lce_forward_stats")
+
+    for _ in range(3):
+        fwd_kernel()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        fwd_kernel()
+    k1.record()
+    torch.cuda.synchronize()
+    ms_fwd = k0.elapsed_time(k1) / args.steps
+
+    status = _lib.device_status()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    flops_step = 8.0 * n * h * v / world          # algorithmic FLOPs per GPU per step
+    tf_step = flops_step / (ms_step * 1e-3) / 1e12
+    flops_fwd = 2.0 * n * h * v_loc
+    tf_fwd = flops_fwd / (ms_fwd * 1e-3) / 1e12
+    base = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample_rows = max(16, min(n, int(1.5e12 / (8.0 * h * v))))
+        base = cpu_baseline(data, sample_rows, repeats=3, warmup=1)
+        base = {k: base[k] for k in ("value", "unit", "cores", "host_cpus", "kind", "sample")}
+    line = {
+        "metric": METRIC, "value": n / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens": n, "hidden": h, "vocab": v, "vocab_per_gpu": v_loc,
+                   "reduction": red, "parallelism": f"vocab-parallel x{world}",
+                   "l2": "weight shard (%.0f MB) exceeds L2, no explicit flush" % (v_loc * h * 2 / 1e6)},
+        "loss": loss_value,
+        "device_status": status,
+        "step_tflops_per_gpu": tf_step,
+        "step_frac_of_peak": {"burst_%g" % peaks["burst"]: tf_step / peaks["burst"],
+                              "sustained_%g" % peaks["sustained"]: tf_step / peaks["sustained"],
+                              "nominal_2250": tf_step / 2250.0},
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<EpiStats> (forward logits + softmax statistics)",
+                     "achieved": tf_fwd, "peak": peaks["burst"], "peak_source": peaks["source"] + " burst",
+                     "unit": "TFLOP/s", "frac": tf_fwd / peaks["burst"], "ms_per_launch": ms_fwd,
+                     "flops_per_launch": flops_fwd, "traffic": None},
+        "e2e": {"value": n / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + t_host.numel() * t_host.element_size(),
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if base is not None:
+        line["cpu_baseline"] = base
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default="llama3-8b",
+                    help="llama3-8b (headline), gpt2-small, large-vocab, 14b-class, sweep-<rows>")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@ REDUCTIONS = {"none": REDUCTION_NONE, "mean": REDUCTION_MEAN, "sum": REDUCTION_S
 SIGNATURES = {
     "lce_version": (c_int, []),
     "lce_strerror": (c_char_p, [c_int]),
+    "lce_launch_count": (ctypes.c_ulonglong, []),
     "lce_device_status": (c_int, [ctypes.POINTER(c_int), c_int]),
     "lce_forward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
     "lce_forward_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,

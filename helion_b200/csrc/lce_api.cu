@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -31,6 +32,8 @@ struct DeviceInfo {
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mutex;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::atomic<unsigned long long> g_launches{0};  // kernels this library has launched (all devices)
+#define LCE_COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
 
 int device_info(DeviceInfo** out) {
     int dev = 0;
@@ -113,6 +116,7 @@ int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long
     kern<<<grid, kGemmThreads, smem, stream>>>(tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks),
                                                m_fastest, ep, d.status_ptr);
+    LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
@@ -135,6 +139,7 @@ int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool
     const int grid = static_cast<int>(m_tiles * n_tiles < cap ? m_tiles * n_tiles : cap);
     gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(
         A, B, static_cast<int>(K), static_cast<int>(m_tiles), static_cast<int>(n_tiles), ep);
+    LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
@@ -205,6 +210,7 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
     const int threads = 256;
     merge_partials_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, stream>>>(
         static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), stats);
+    LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
@@ -377,6 +383,8 @@ extern "C" {
 
 int lce_version(void) { return LCE_VERSION; }
 
+unsigned long long lce_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
 const char* lce_strerror(int code) {
     switch (code) {
         case LCE_OK: return "ok";
@@ -458,12 +466,14 @@ int lce_finalize(const float* stats, int R, const void* target, int target_is_i6
         const int threads = 256;
         finalize_rows_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, s>>>(
             stats, R, target, target_is_i64, static_cast<int>(N), ignore_index, lse, loss_rows);
+        LCE_COUNT_LAUNCH();
         if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     }
     if (reduction != LCE_REDUCTION_NONE || valid_count) {
         reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
                                               reduction == LCE_REDUCTION_MEAN ? 1 : 0,
                                               reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
+        LCE_COUNT_LAUNCH();
         if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     }
     return LCE_OK;
@@ -508,11 +518,13 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     float* rowscale = reinterpret_cast<float*>(wsc + p.off_rowscale);
     if (reduction == LCE_REDUCTION_MEAN) {
         count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
+        LCE_COUNT_LAUNCH();
         if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     }
     rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
         target, target_is_i64, static_cast<int>(N), ignore_index, grad_out,
         reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0, count, rowscale);
+    LCE_COUNT_LAUNCH();
     if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
 #define LCE_BWD(T)                                                                                          \

@@ -60,6 +60,11 @@ extern "C" {
 int lce_version(void);
 const char* lce_strerror(int code);
 
+/* Number of kernels this library has launched since it was loaded (host-side counter, all devices
+ * and streams). Lets a harness state how many of the library's own kernels ran inside a timed
+ * region. No counterpart in the reference. */
+unsigned long long lce_launch_count(void);
+
 /* Reads (and optionally clears) the per-device status word that kernels set when one of their
  * bounded waits ran out (0 = no such event). Synchronises the device; meant for tests. */
 int lce_device_status(int* status_out, int clear);
