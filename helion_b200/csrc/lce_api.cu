@@ -220,8 +220,8 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
 // G = dLoss/dLogits is produced one block [nr rows x nc vocab columns] at a time and consumed at
 // once by the dW and dX GEMMs. A block spanning all rows (vocab bands) completes dW[band] in one
 // launch and sums dX over bands; a block spanning the whole vocabulary (row chunks) completes
-// dX[chunk] and sums dW over chunks. The plan takes whichever moves fewer fp32 partial sums and
-// falls back to a 2-D grid of blocks when neither fits the byte cap.
+// dX[chunk] and sums dW over chunks; in general the blocks form a 2-D grid and both are summed.
+// The plan takes the block shape under the byte cap that moves the fewest fp32 partial sums.
 struct BwdPlan {
     long long nr, nc;          // block shape (last blocks may be smaller)
     long long n_rblk, n_cblk;  // number of row chunks / vocab bands
@@ -242,23 +242,28 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
         p.nr = N > 0 ? N : 1;
         p.nc = V;
     } else {
-        long long nc_band = static_cast<long long>(cap / (static_cast<size_t>(N) * e)) / col_q * col_q;
-        long long nr_chunk = static_cast<long long>(cap / (static_cast<size_t>(V) * e)) / row_q * row_q;
-        const bool band_ok = nc_band >= col_q, chunk_ok = nr_chunk >= row_q;
-        // fp32 partial-sum traffic (read + write) each choice causes
-        const double cost_band = band_ok ? (cdiv(V, nc_band) - 1) * 8.0 * N * H * (need_dx ? 1 : 0) : 1e300;
-        const double cost_chunk = chunk_ok ? (cdiv(N, nr_chunk) - 1) * 8.0 * V * H * (need_dw ? 1 : 0) : 1e300;
-        if (band_ok && cost_band <= cost_chunk) {
-            p.nr = N;
-            p.nc = nc_band;
-        } else if (chunk_ok) {
-            p.nr = nr_chunk;
-            p.nc = V;
-        } else {
-            p.nr = 8192 < N ? 8192 : N;
-            p.nc = static_cast<long long>(cap / (static_cast<size_t>(p.nr) * e)) / col_q * col_q;
-            if (p.nc < col_q) p.nc = col_q;
-            if (p.nc > V) p.nc = V;
+        // Candidates: all rows, or 128 * 2^k rows; the band is as wide as the cap then allows
+        // (multiples of 256 columns, at least 256). Cost = bytes of fp32 partial sums re-read and
+        // re-written: dX once per extra vocab band, dW once per extra row chunk.
+        double best = 1e300;
+        for (long long nr = N;;) {
+            long long nc = static_cast<long long>(cap / (static_cast<size_t>(nr) * e)) / col_q * col_q;
+            if (nc < col_q) nc = col_q;
+            if (nc > V) nc = V;
+            if (static_cast<size_t>(nr) * nc * e <= cap || nr <= row_q) {
+                const double cost = (cdiv(V, nc) - 1) * 8.0 * N * H * (need_dx ? 1 : 0) +
+                                    (cdiv(N, nr) - 1) * 8.0 * V * H * (need_dw ? 1 : 0);
+                if (cost < best) {
+                    best = cost;
+                    p.nr = nr;
+                    p.nc = nc;
+                }
+            }
+            if (nr <= row_q) break;
+            // next candidate: the largest 128 * 2^k below nr
+            long long next = row_q;
+            while (next * 2 < nr) next *= 2;
+            nr = next;
         }
     }
     p.n_rblk = N > 0 ? cdiv(N, p.nr) : 0;

@@ -35,6 +35,8 @@ class HeadConfig:
 
 
 CONFIGS = {
+    # seconds-sized workload for harness self-tests
+    "smoke": HeadConfig("smoke", 1, 256, 128, 1000, zipf=True, ignore_frac=0.02),
     # GPT-2-small head; the one case small enough to run in full on the CPU
     "gpt2-small": HeadConfig("gpt2-small", 4, 1024, 768, 50304, target_max=50257, unit_rms=False,
                              ignore_frac=0.01),

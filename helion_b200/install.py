@@ -10,6 +10,7 @@ enough to make training scripts, examples and tests run on the sm_100a kernels u
 from __future__ import annotations
 
 import importlib
+import sys
 from types import ModuleType
 
 from . import ops
@@ -21,16 +22,20 @@ _saved: dict[tuple[str, str], object] = {}
 
 
 def _targets(root: ModuleType | None) -> list[ModuleType]:
-    if root is not None:
-        mods = [root]
-        sub = getattr(root, "ops", None)
-        if isinstance(sub, ModuleType):
-            mods.append(sub)
-            leaf = getattr(sub, "cross_entropy", None)
-            if isinstance(leaf, ModuleType):
-                mods.append(leaf)
-        return mods
-    return [importlib.import_module(name) for name in MODULES]
+    # `tritium.ops.cross_entropy` as an attribute is the re-exported plain cross_entropy FUNCTION
+    # (tritium/ops/__init__.py), so the submodules are taken from the import system, not via getattr.
+    base = MODULES[0] if root is None else root.__name__
+    mods = [importlib.import_module(base) if root is None else root]
+    for suffix in (".ops", ".ops.cross_entropy"):
+        name = base + suffix
+        mod = sys.modules.get(name)
+        if mod is None:
+            try:
+                mod = importlib.import_module(name)
+            except ImportError:
+                continue
+        mods.append(mod)
+    return mods
 
 
 def install(tritium_module: ModuleType | None = None) -> list[str]:

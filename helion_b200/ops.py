@@ -21,7 +21,7 @@ from typing import Any
 
 import torch
 
-from . import _lib
+from . import _lib, parallel
 
 FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
 INDEX_DTYPES = (torch.int32, torch.int64)
@@ -145,17 +145,6 @@ def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
-# ----------------------------------------------------------------------------------------------
-# vocabulary sharding helpers
-# ----------------------------------------------------------------------------------------------
-def _group_info(process_group: Any) -> tuple[int, int]:
-    if process_group is None:
-        return 0, 1
-    import torch.distributed as dist
-
-    return dist.get_rank(process_group), dist.get_world_size(process_group)
-
-
 def _resolve_vocab_start(vocab_start: int | None, rank: int, v_local: int) -> int:
     # contiguous equal shards unless the caller says where this shard begins
     return rank * v_local if vocab_start is None else int(vocab_start)
@@ -215,20 +204,12 @@ def _forward(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, r
         shape = tuple(target.shape) if red == _lib.REDUCTION_NONE else ()
         return (torch.zeros(shape, dtype=torch.float32, device=dev),
                 torch.empty((0,), dtype=torch.float32, device=dev))
-    rank, world = _group_info(process_group)
+    rank, world = parallel.group_rank_size(process_group)
     hidden2d = hidden.view(n_rows, hidden_size)
     target1d = target.view(n_rows)
     stats = local_stats(hidden2d, weight, target1d, _resolve_vocab_start(vocab_start, rank, v_local),
                         _path_flags())
-    if world > 1:
-        import torch.distributed as dist
-
-        gathered = torch.empty((world, 3, n_rows), dtype=torch.float32, device=dev)
-        dist.all_gather_into_tensor(gathered, stats, group=process_group)
-        stats3 = gathered
-    else:
-        stats3 = stats.view(1, 3, n_rows)
-    loss, lse, _ = finalize(stats3, target1d, reduction, ignore_index)
+    loss, lse, _ = finalize(parallel.gather_stats(stats, process_group), target1d, reduction, ignore_index)
     if red == _lib.REDUCTION_NONE:
         loss = loss.view(target.shape)
     return loss, lse
@@ -245,7 +226,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     n_rows, hidden_size = hidden2d.shape
     v_local = weight.shape[0]
     dev = hidden2d.device
-    rank, world = _group_info(process_group)
+    rank, world = parallel.group_rank_size(process_group)
     sharded = world > 1 and reduce_dx
     L = _lib.lib()
 
@@ -282,10 +263,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
             "lce_backward",
         )
     if sharded and dx is not None:
-        import torch.distributed as dist
-
-        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=process_group)
-        dx = dx.to(hidden2d.dtype)
+        dx = parallel.reduce_dx(dx, hidden2d.dtype, process_group)
     return dx, dw
 
 

@@ -1,0 +1,64 @@
+"""Vocabulary-parallel plumbing: one process per GPU, weight rows sharded contiguously by vocabulary.
+
+The reference is single-GPU (it has no torch.distributed code at all), so this layer has no reference
+counterpart; its contract is "the same numbers as one GPU". Forward: every rank computes softmax
+statistics (max, sum-exp, target logit) of its shard, ONE collective exchanges those 3 floats per row,
+and every rank merges them in rank order, so all ranks hold bit-identical losses. Backward: dW is local;
+the partial dX = G_r @ W_r of each rank is summed over the group in fp32 and rounded once.
+
+The functions below touch no kernels and work on any backend (NCCL on GPUs, gloo on CPU tensors in
+tests); ops.py calls them between the kernel launches.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+
+def group_rank_size(process_group: Any) -> tuple[int, int]:
+    if process_group is None:
+        return 0, 1
+    import torch.distributed as dist
+
+    return dist.get_rank(process_group), dist.get_world_size(process_group)
+
+
+def shard_bounds(vocab_size: int, world_size: int, rank: int) -> tuple[int, int]:
+    """Rows ``[start, end)`` of the full weight that ``rank`` owns: equal contiguous shards, the last
+    ranks one row shorter when the vocabulary does not divide evenly."""
+    base, extra = divmod(vocab_size, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def shard_weight(weight: torch.Tensor, process_group: Any) -> tuple[torch.Tensor, int]:
+    """This rank's contiguous slice of a full ``[V, H]`` weight and its first global row."""
+    rank, world = group_rank_size(process_group)
+    start, end = shard_bounds(weight.shape[0], world, rank)
+    return weight[start:end].contiguous(), start
+
+
+def gather_stats(stats: torch.Tensor, process_group: Any) -> torch.Tensor:
+    """``[3, N]`` local statistics -> ``[R, 3, N]`` ordered by rank (one all-gather of 12 bytes per row)."""
+    rank, world = group_rank_size(process_group)
+    if world == 1:
+        return stats.unsqueeze(0)
+    import torch.distributed as dist
+
+    out = torch.empty((world,) + tuple(stats.shape), dtype=stats.dtype, device=stats.device)
+    # the output is the concatenation of the inputs along dim 0: [R*3, N] viewed as [R, 3, N]
+    dist.all_gather_into_tensor(out.view((world * stats.shape[0],) + tuple(stats.shape[1:])), stats.contiguous(),
+                                group=process_group)
+    return out
+
+
+def reduce_dx(dx_partial: torch.Tensor, out_dtype: torch.dtype, process_group: Any) -> torch.Tensor:
+    """Sum the fp32 partial ``dX`` of all ranks and round to ``out_dtype`` once."""
+    rank, world = group_rank_size(process_group)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(dx_partial, op=dist.ReduceOp.SUM, group=process_group)
+    return dx_partial if dx_partial.dtype == out_dtype else dx_partial.to(out_dtype)
