@@ -26,6 +26,9 @@ SIGNATURES = {
     "lce_forward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
     "lce_forward_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
                                   c_int, c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
+    "lce_forward_stats_static_capacity": (c_size_t, []),
+    "lce_forward_stats_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
+                                         c_int, c_void_p, c_uint, c_void_p]),
     "lce_finalize_workspace_bytes": (c_size_t, [c_int64]),
     "lce_finalize": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_size_t, c_void_p]),

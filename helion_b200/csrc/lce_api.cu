@@ -399,6 +399,8 @@ const char* lce_strerror(int code) {
         case LCE_ERR_ARCH: return "device is not compute capability 10.x (sm_100a only, no fallback)";
         case LCE_ERR_CUDA: return "CUDA runtime or driver call failed";
         case LCE_ERR_TOO_LARGE: return "dimension too large for 32-bit tile indexing";
+        case LCE_ERR_STATIC_SCRATCH:
+            return "problem needs more than the 16 MiB of built-in scratch; use lce_forward_stats with a workspace";
         default: return "unknown error";
     }
 }
@@ -570,6 +572,71 @@ int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t 
     if (a_mn && !b_mn) return LCE_DBG(true, false);
     return LCE_DBG(true, true);
 #undef LCE_DBG
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Forward statistics with library-owned scratch (no allocation by anyone at call time)
+// ---------------------------------------------------------------------------------------------
+namespace lce {
+namespace {
+
+// Scratch for the per-(vocab tile, row) partial statistics of lce_forward_stats_static. It is part
+// of the library image: every GPU that loads the library carries these 16 MiB until the process
+// exits. In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+constexpr size_t kStaticScratchBytes = 16ull << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Resolves the device address of g_static_scratch once per device (the device must be current).
+int static_scratch_address(void** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LCE_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return LCE_ERR_ARG;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return LCE_ERR_CUDA;
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return LCE_OK;
+}
+
+}  // namespace
+}  // namespace lce
+
+extern "C" {
+
+size_t lce_forward_stats_static_capacity(void) { return lce::kStaticScratchBytes; }
+
+int lce_forward_stats_static(const void* x, const void* w, const void* target, int target_is_i64, int64_t N,
+                             int64_t H, int64_t V, int64_t vocab_start, int dtype, float* stats, unsigned flags,
+                             void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (N == 0) return LCE_OK;
+    if (!x || !w || !target || !stats) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    if (fwd_layout(N, V, use_tc).bytes > kStaticScratchBytes) return LCE_ERR_STATIC_SCRATCH;
+    void* scratch = nullptr;
+    if ((rc = static_scratch_address(&scratch))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Nothing in the scratch has to start at zero: the GEMM epilogue writes every (tile, row) entry
+    // the merge kernel reads, earlier in this same call and on the same stream.
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+        case LCE_DTYPE_F16:
+            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+        default:
+            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+    }
 }
 
 }  // extern "C"

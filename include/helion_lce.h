@@ -56,6 +56,7 @@ extern "C" {
 #define LCE_ERR_ARCH 4         /* current device is not compute capability 10.x                  */
 #define LCE_ERR_CUDA 5         /* a CUDA runtime / driver call failed                            */
 #define LCE_ERR_TOO_LARGE 6    /* a dimension exceeds what 32-bit tile indexing supports         */
+#define LCE_ERR_STATIC_SCRATCH 7 /* lce_forward_stats_static: problem exceeds the built-in scratch  */
 
 int lce_version(void);
 const char* lce_strerror(int code);
@@ -80,6 +81,31 @@ size_t lce_forward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dt
 int lce_forward_stats(const void* x, const void* w, const void* target, int target_is_i64,
                       int64_t N, int64_t H, int64_t V_local, int64_t vocab_start, int dtype,
                       float* stats, void* ws, size_t ws_bytes, unsigned flags, void* stream);
+
+/* Same computation and same `stats` output as lce_forward_stats, but with no workspace argument:
+ * the partial statistics go through a fixed 16 MiB array that is compiled into the library
+ * (lce_forward_stats_static_capacity() returns its size). No counterpart in the reference.
+ *
+ * It exists for hosts that cannot hand the library scratch memory at call time - a serving or
+ * training process whose device memory was carved up once at start-up, so that a later allocation
+ * would fail or fragment someone else's pool, or a thread that must not block on the device-wide
+ * synchronisation an allocation can imply. The call itself allocates nothing and frees nothing, on
+ * the device or through any library.
+ *
+ *   - Limit: ceil(V_local / T) * 3 * roundup(N, 64) * 4 bytes must fit in the 16 MiB, with T = 256 on
+ *     the tcgen05 path and 32 on the CUDA-core path (e.g. N = 4096 with V_local = 50304 in bf16).
+ *     Larger problems return LCE_ERR_STATIC_SCRATCH and launch nothing.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture. Later calls reuse the cached address.
+ *   - Every GPU that loads the library holds the 16 MiB until the process exits.
+ *   - All calls on a device share the one array, which still holds the previous call's values. No
+ *     entry needs clearing: each value read was written earlier in the same call. But two calls
+ *     that can overlap on the GPU (different streams, no dependency) would race on it; serialise
+ *     them, or use lce_forward_stats with separate workspaces. */
+size_t lce_forward_stats_static_capacity(void);
+int lce_forward_stats_static(const void* x, const void* w, const void* target, int target_is_i64,
+                             int64_t N, int64_t H, int64_t V_local, int64_t vocab_start, int dtype,
+                             float* stats, unsigned flags, void* stream);
 
 /* Replaces _linear_cross_entropy_reduce_forward_kernel (tritium/ops/cross_entropy.py:251-293):
  * merges the statistics of R shards (stats is [R][3][N], shard r at stats + r*3*N; R = 1 on one
