@@ -207,8 +207,7 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
         rc = launch_simt<T, EpiStats>(d, a, false, b, false, N, V, H, ep, stream);
     }
     if (rc) return rc;
-    const int threads = 256;
-    merge_partials_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, stream>>>(
+    merge_partials_kernel<<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, stream>>>(
         static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), stats);
     LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;

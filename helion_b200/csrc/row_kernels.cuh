@@ -6,27 +6,49 @@
 
 namespace lce {
 
+// Merges two (max, sum-exp) pairs; the sum is expressed relative to the new max.
+__device__ __forceinline__ void merge_ms(float& m, float& s, float bm, float bs) {
+    const float nm = fmaxf(m, bm);
+    if (nm != -INFINITY) s = s * ptx::ex2((m - nm) * kLog2e) + bs * ptx::ex2((bm - nm) * kLog2e);
+    m = nm;
+}
+
 // partial: [n_tiles][3][row_stride]  ->  stats: [3][N]
-// Merge order is ascending tile index, the same on every run.
-__global__ void merge_partials_kernel(const float* __restrict__ partial, int n_tiles,
-                                      long long row_stride, int N, float* __restrict__ stats) {
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
-    if (row >= N) return;
+// One CTA = 32 rows x 32 tile lanes: lane j folds tiles j, j+32, ... in ascending order, then the 32
+// lane results are folded in lane order by the first warp. Loads are 128-byte coalesced along the
+// rows; the merge order depends only on n_tiles, so the result is the same on every run.
+constexpr int kMergeRows = 32;
+constexpr int kMergeLanes = 32;
+
+__global__ void __launch_bounds__(kMergeRows * kMergeLanes)
+merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N,
+                      float* __restrict__ stats) {
+    __shared__ float sm[kMergeLanes][kMergeRows + 1], ss[kMergeLanes][kMergeRows + 1],
+        st[kMergeLanes][kMergeRows + 1];
+    const int r = threadIdx.x % kMergeRows;
+    const int j = threadIdx.x / kMergeRows;
+    const int row = blockIdx.x * kMergeRows + r;
     float m = -INFINITY, s = 0.f, t = -INFINITY;
-    for (int b = 0; b < n_tiles; ++b) {
-        const float* base = partial + static_cast<long long>(b) * 3 * row_stride + row;
-        const float bm = base[0];
-        const float bs = base[row_stride];
-        const float bt = base[2 * row_stride];
-        const float nm = fmaxf(m, bm);
-        if (nm != -INFINITY)
-            s = s * ptx::ex2((m - nm) * kLog2e) + bs * ptx::ex2((bm - nm) * kLog2e);
-        m = nm;
-        t = fmaxf(t, bt);
+    if (row < N) {
+        for (int b = j; b < n_tiles; b += kMergeLanes) {
+            const float* base = partial + static_cast<long long>(b) * 3 * row_stride + row;
+            merge_ms(m, s, base[0], base[row_stride]);
+            t = fmaxf(t, base[2 * row_stride]);
+        }
     }
-    stats[row] = m;
-    stats[static_cast<long long>(N) + row] = s;
-    stats[2ll * N + row] = t;
+    sm[j][r] = m;
+    ss[j][r] = s;
+    st[j][r] = t;
+    __syncthreads();
+    if (j == 0 && row < N) {
+        for (int k = 1; k < kMergeLanes; ++k) {
+            merge_ms(m, s, sm[k][r], ss[k][r]);
+            t = fmaxf(t, st[k][r]);
+        }
+        stats[row] = m;
+        stats[static_cast<long long>(N) + row] = s;
+        stats[2ll * N + row] = t;
+    }
 }
 
 // stats: [R][3][N] -> lse[N], per-row loss (0 for ignored rows).
@@ -43,10 +65,7 @@ __global__ void finalize_rows_kernel(const float* __restrict__ stats, int R, con
         const float bm = base[0];
         const float bs = base[N];
         const float bt = base[2ll * N];
-        const float nm = fmaxf(m, bm);
-        if (nm != -INFINITY)
-            s = s * ptx::ex2((m - nm) * kLog2e) + bs * ptx::ex2((bm - nm) * kLog2e);
-        m = nm;
+        merge_ms(m, s, bm, bs);
         t = fmaxf(t, bt);
     }
     const float l = m + logf(s);
