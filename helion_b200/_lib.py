@@ -13,7 +13,7 @@ from . import build as _build
 
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 REDUCTION_NONE, REDUCTION_MEAN, REDUCTION_SUM = 0, 1, 2
-FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_DX_F32, FLAG_NO_DX, FLAG_NO_DW = 1, 2, 4, 8, 16
+FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_DX_F32, FLAG_NO_DX, FLAG_NO_DW, FLAG_ONE_CTA = 1, 2, 4, 8, 16, 32
 
 REDUCTIONS = {"none": REDUCTION_NONE, "mean": REDUCTION_MEAN, "sum": REDUCTION_SUM}
 
@@ -37,7 +37,7 @@ SIGNATURES = {
                              c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
                              c_uint, c_size_t, c_void_p]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
-                               c_void_p]),
+                               c_uint, c_void_p]),
 }
 
 

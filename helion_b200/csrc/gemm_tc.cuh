@@ -15,18 +15,33 @@
 //   warps 2-5   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
 // Pipelines: STAGES-deep smem ring (full/empty mbarriers) between producer and issuer, and two
 // accumulator buffers in TMEM (tmem_full/tmem_empty) so the epilogue of tile i overlaps the main
-// loop of tile i+1. Tiles are dealt round-robin to a grid of (at most) one CTA per SM.
+// loop of tile i+1. Tiles are dealt round-robin to a persistent grid.
+//
+// Two variants, selected by CG:
+//   CG = 1  one CTA per tile: tcgen05.mma.cta_group::1, M = 128. 48 KB per stage (A 16 + B 32).
+//   CG = 2  a CTA PAIR (cluster of 2 on one TPC) per 256 x BN tile: tcgen05.mma.cta_group::2 with
+//           M = 256, issued by the even CTA for both. Each CTA loads its own 128 rows of A and
+//           only HALF of the B tile (BN/2 rows); the tensor cores of the pair read both halves.
+//           Per FLOP that is 2/3 of the shared-memory fill and L2 traffic of CG = 1, and the
+//           32 KB stages leave room for a deeper ring. No TMA multicast is used: every copy lands
+//           in the shared memory of the CTA that issued it. Cross-CTA signalling:
+//             full[s]   lives in the leader: its producer announces the bytes of BOTH CTAs'
+//                       copies there and both CTAs' copies count on it (the peer's producer only
+//                       issues copies; it can do so as soon as its own empty[s] fires, which the
+//                       same commit fires in both CTAs, so the phase it signals is always open);
+//             empty[s], tmem_full[b]  local to each CTA; the leader's tcgen05.commit arrives on
+//                       the barrier at that offset in both CTAs;
+//             tmem_empty[b]  lives in the leader; the epilogue warps of both CTAs arrive on it.
 #pragma once
 
 #include "ptx.cuh"
 
 namespace lce {
 
-constexpr int kBM = 128;      // accumulator tile rows  (= TMEM lanes)
+constexpr int kBM = 128;      // accumulator tile rows per CTA (= TMEM lanes)
 constexpr int kBK = 64;       // k elements per pipeline stage (= one 128-byte swizzle row)
 constexpr int kUmmaK = 16;    // k elements per tcgen05.mma for 16-bit operands
 constexpr int kGemmThreads = 192;
-constexpr int kEpiWarp0 = 2;
 
 // error codes written to the device status word
 constexpr int kDevErrProducerTimeout = 101;
@@ -34,17 +49,18 @@ constexpr int kDevErrMmaTimeout = 102;
 constexpr int kDevErrEpilogueTimeout = 103;
 
 struct TileCtx {
-    int m_tile;       // tile row index
+    int m_tile;       // 128-row tile index
     int n_tile;       // tile column index
     int n_tiles;      // tile columns in the problem
     int row_in_tile;  // 0..127, the row this thread owns
     int bn;           // tile width in columns
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CG>
 struct GemmSmem {
     static constexpr int kABytes = kBM * kBK * 2;
-    static constexpr int kBBytes = BN * kBK * 2;
+    static constexpr int kBRows = BN / CG;  // B rows (n indices) this CTA stages
+    static constexpr int kBBytes = kBRows * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 256;
     // 1024 bytes of slack so the ring can be aligned to the swizzle atom by hand
@@ -64,16 +80,21 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+// m_tiles counts 128-row tiles. With CG = 2 the scheduler deals out pairs of them: unit u covers
+// m tiles 2u and 2u+1 (the second may lie past the end of the matrix: its loads return zeros
+// and the epilogues skip its rows).
+template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                int m_tiles, int n_tiles, int k_blocks, int m_fastest,
                const typename Epi::Params ep, int* __restrict__ status) {
-    using S = GemmSmem<BN, STAGES>;
-    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width");
+    using S = GemmSmem<BN, STAGES, CG>;
+    static_assert(CG == 1 || CG == 2, "cta group");
+    static_assert(BN % (64 * CG) == 0 && BN >= 64 && BN <= 256, "tile width");
     static_assert(2 * BN <= 512, "two accumulator buffers must fit in tensor memory");
     constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
-    constexpr uint32_t kIdesc = ptx::make_idesc_f16(kBM, BN, IS_BF16, A_MN, B_MN);
+    constexpr uint32_t kIdesc = ptx::make_idesc_f16(kBM * CG, BN, IS_BF16, A_MN, B_MN);
+    constexpr bool kPair = CG == 2;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -92,16 +113,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;  // 0 = leader of the pair
+    const int unit0 = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int unit_step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
+    const int total_units = m_units * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(full_bar(s), 1);  // the (leader's) producer; copies count bytes on it
             ptx::mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
-            ptx::mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+            ptx::mbar_init(tempty_bar(b), 4 * CG);  // one arrival per epilogue warp of the group
         }
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -110,11 +135,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ptx::prefetch_tensormap(&tmB);
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
-        ptx::tmem_relinquish();
+        if constexpr (kPair) {
+            ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (kPair) ptx::cluster_sync_all();  // the peer's barriers exist before anyone signals them
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -123,9 +154,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (ptx::elect_one()) {
             uint32_t issued = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                int m_tile, n_tile;
-                tile_coords(tile, m_tiles, n_tiles, m_fastest, m_tile, n_tile);
+            const uint32_t leader_full0 = kPair ? ptx::map_to_cta(full_bar(0), 0) : 0u;
+            for (int unit = unit0; unit < total_units && ok; unit += unit_step) {
+                int m_unit, n_tile;
+                tile_coords(unit, m_units, n_tiles, m_fastest, m_unit, n_tile);
+                const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
+                const int b_row0 = n_tile * BN + static_cast<int>(cta_rank) * S::kBRows;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t stage = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1u;
@@ -135,46 +169,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     const uint32_t sa = smem_base + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+                    // the barrier the MMA issuer waits on: our own, or the leader's for a pair
+                    const uint32_t fb = kPair ? leader_full0 + 8u * stage : full_bar(stage);
+                    auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+                        if constexpr (kPair) ptx::tma_load_2d_pair(dst, tm, fb, x, y);
+                        else ptx::tma_load_2d(dst, tm, fb, x, y);
+                    };
+                    // bytes of the whole group's copies for this stage, announced by the leader only
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes * CG);
                     if constexpr (!A_MN) {
-                        ptx::tma_load_2d(sa, &tmA, full_bar(stage), kb * kBK, m_tile * kBM);
+                        load(sa, &tmA, kb * kBK, m_tile * kBM);
                     } else {
 #pragma unroll
                         for (int j = 0; j < kBM / 64; ++j)
-                            ptx::tma_load_2d(sa + j * (kBK * 128), &tmA, full_bar(stage),
-                                             m_tile * kBM + j * 64, kb * kBK);
+                            load(sa + j * (kBK * 128), &tmA, m_tile * kBM + j * 64, kb * kBK);
                     }
                     if constexpr (!B_MN) {
-                        ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n_tile * BN);
+                        load(sb, &tmB, kb * kBK, b_row0);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_2d(sb + j * (kBK * 128), &tmB, full_bar(stage),
-                                             n_tile * BN + j * 64, kb * kBK);
+                        for (int j = 0; j < S::kBRows / 64; ++j)
+                            load(sb + j * (kBK * 128), &tmB, b_row0 + j * 64, kb * kBK);
                     }
                     ++issued;
                 }
             }
             if (!ok || *abort_flag) {
-                // Unwinding: let every copy already in flight land before the CTA retires.
+                // Unwinding: give every copy already in flight time to land before the CTA retires.
                 if (!ok) atomicCAS(status, 0, kDevErrProducerTimeout);
-                const uint32_t back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
-                for (uint32_t j = 1; j <= back; ++j) {
-                    const uint32_t i = issued - j;
-                    const uint32_t bar = full_bar(i % STAGES);
-                    const uint32_t par = (i / STAGES) & 1u;
-                    for (int spin = 0; spin < (1 << 16); ++spin)
-                        if (ptx::mbar_try_wait(bar, par)) break;
+                if constexpr (!kPair) {
+                    const uint32_t back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+                    for (uint32_t j = 1; j <= back; ++j) {
+                        const uint32_t i = issued - j;
+                        const uint32_t bar = full_bar(i % STAGES);
+                        const uint32_t par = (i / STAGES) & 1u;
+                        for (int spin = 0; spin < (1 << 16); ++spin)
+                            if (ptx::mbar_try_wait(bar, par)) break;
+                    }
+                } else {
+                    // the completion barrier may be the peer's: wait out the copy latency instead
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (ptx::globaltimer_ns() - t0 < 200000ull) {
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (ptx::elect_one()) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (cta_rank == 0 && ptx::elect_one()) {
             uint32_t consumed = 0;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int unit = unit0; unit < total_units && ok; unit += unit_step, ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
                 const uint32_t buf_phase = (local_tile >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty_bar(buf), buf_phase ^ 1u, abort_flag)) {
@@ -203,17 +249,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const uint64_t db =
                             B_MN ? ptx::make_smem_desc(sb + k * (kUmmaK * 128), kBK * 128, 1024)
                                  : ptx::make_smem_desc(sb + k * (kUmmaK * 2), 0, 1024);
-                        ptx::umma_f16(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        if constexpr (kPair) ptx::umma_f16_pair(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        else ptx::umma_f16(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    ptx::umma_commit(empty_bar(stage));  // smem slot reusable once these MMAs retire
+                    // smem slot reusable (in both CTAs of a pair) once these MMAs retire
+                    if constexpr (kPair) ptx::umma_commit_pair(empty_bar(stage), 3);
+                    else ptx::umma_commit(empty_bar(stage));
                     ++consumed;
                 }
-                if (ok) ptx::umma_commit(tfull_bar(buf));  // accumulator complete
+                if (ok) {  // accumulator complete
+                    if constexpr (kPair) ptx::umma_commit_pair(tfull_bar(buf), 3);
+                    else ptx::umma_commit(tfull_bar(buf));
+                }
             }
             if (!ok || *abort_flag) {
                 if (!ok) atomicCAS(status, 0, kDevErrMmaTimeout);
                 // Unwinding: wait (bounded) for the MMAs already issued before TMEM is freed.
-                ptx::umma_commit(drain_bar);
+                if constexpr (kPair) ptx::umma_commit_pair(drain_bar, 1);
+                else ptx::umma_commit(drain_bar);
                 for (int spin = 0; spin < (1 << 16); ++spin)
                     if (ptx::mbar_try_wait(drain_bar, 0)) break;
             }
@@ -224,9 +277,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t local_tile = 0;
         bool ok = true;
         typename Epi::State st;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-            int m_tile, n_tile;
-            tile_coords(tile, m_tiles, n_tiles, m_fastest, m_tile, n_tile);
+        for (int unit = unit0; unit < total_units && ok; unit += unit_step, ++local_tile) {
+            int m_unit, n_tile;
+            tile_coords(unit, m_units, n_tiles, m_fastest, m_unit, n_tile);
+            const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
             const uint32_t buf = local_tile & 1u;
             const uint32_t buf_phase = (local_tile >> 1) & 1u;
             TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN};
@@ -244,10 +298,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ptx::tmem_ld_wait();
                 Epi::chunk(st, ep, tc, c * 32, v);
             }
-            // all TMEM reads of this buffer are done: hand it back before touching global memory
+            // all TMEM reads of this buffer are done: hand it back to the MMA issuer
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            if (lane == 0) {
+                if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
+                else ptx::mbar_arrive(tempty_bar(buf));
+            }
             Epi::end(st, ep, tc);
         }
         if (!ok && lane == 0) atomicCAS(status, 0, kDevErrEpilogueTimeout);
@@ -255,9 +312,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (kPair) ptx::cluster_sync_all();  // neither CTA leaves while its peer may still touch it
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+        else ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

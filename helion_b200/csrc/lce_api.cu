@@ -19,7 +19,8 @@ __device__ int g_device_status = 0;
 namespace {
 
 constexpr int kBN = 256;
-constexpr int kStages = 4;
+constexpr int kStages1 = 4;  // 48 KB stages, one CTA per tile
+constexpr int kStages2 = 6;  // 32 KB stages, CTA pair per tile
 constexpr size_t kDefaultBlockBytes = 256ull << 20;
 constexpr int kMaxDevices = 64;
 
@@ -29,6 +30,9 @@ struct DeviceInfo {
     int cc_major = 0;
     int* status_ptr = nullptr;
 };
+
+// Which tcgen05 variant the GEMM launches use; set per call from the flags.
+thread_local int t_cta_group = 2;
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mutex;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -93,31 +97,55 @@ struct Mat {
     long long rows, cols, pitch_elems;
 };
 
-template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
-int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
+template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
+                 int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
+    constexpr int kStages = CG == 2 ? kStages2 : kStages1;
     const int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
     CUtensorMap tma, tmb;
     int rc;
     if (A_MN) rc = make_tmap(&tma, a.ptr, dtype, M, K, a.pitch_elems * 2, 64, kBK);
     else rc = make_tmap(&tma, a.ptr, dtype, K, M, a.pitch_elems * 2, kBK, kBM);
     if (rc) return rc;
+    // each CTA of a pair stages half of the B tile
     if (B_MN) rc = make_tmap(&tmb, b.ptr, dtype, Nn, K, b.pitch_elems * 2, 64, kBK);
-    else rc = make_tmap(&tmb, b.ptr, dtype, K, Nn, b.pitch_elems * 2, kBK, kBN);
+    else rc = make_tmap(&tmb, b.ptr, dtype, K, Nn, b.pitch_elems * 2, kBK, kBN / CG);
     if (rc) return rc;
     const long long m_tiles = cdiv(M, kBM), n_tiles = cdiv(Nn, kBN), k_blocks = cdiv(K, kBK);
-    if (m_tiles * n_tiles > 0x7fffffffll || k_blocks > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
-    if (m_tiles * n_tiles == 0 || k_blocks == 0) return LCE_OK;
-    auto kern = gemm_tc_kernel<kBN, kStages, A_MN, B_MN, IS_BF16, Epi>;
-    constexpr int smem = GemmSmem<kBN, kStages>::kTotalBytes;
+    const long long units = cdiv(m_tiles, CG) * n_tiles;
+    if (m_tiles * n_tiles > 0x3fffffffll || k_blocks > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
+    if (units == 0 || k_blocks == 0) return LCE_OK;
+    auto kern = gemm_tc_kernel<kBN, kStages, CG, A_MN, B_MN, IS_BF16, Epi>;
+    constexpr int smem = GemmSmem<kBN, kStages, CG>::kTotalBytes;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return LCE_ERR_CUDA;
-    const int grid = static_cast<int>(m_tiles * n_tiles < d.sm_count ? m_tiles * n_tiles : d.sm_count);
-    kern<<<grid, kGemmThreads, smem, stream>>>(tma, tmb, static_cast<int>(m_tiles),
-                                               static_cast<int>(n_tiles), static_cast<int>(k_blocks),
-                                               m_fastest, ep, d.status_ptr);
+    const long long slots = d.sm_count / CG;  // one CTA per SM; a pair occupies the two SMs of a TPC
+    const int grid = static_cast<int>(units < slots ? units : slots) * CG;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CG > 1 ? 1 : 0;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
+                                               static_cast<int>(n_tiles), static_cast<int>(k_blocks), m_fastest,
+                                               ep, d.status_ptr);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return err == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
+              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
+    if (t_cta_group == 2)
+        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, ep, stream);
+    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, ep, stream);
 }
 
 template <class T, class Epi>
@@ -148,6 +176,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // The tcgen05 path needs 16-bit inputs, 16-byte aligned bases and row pitches (H % 8 == 0).
 int choose_path(int dtype, long long H, const void* x, const void* w, unsigned flags, bool* use_tc) {
     const bool can_tc = dtype != LCE_DTYPE_F32 && (H % 8) == 0 && aligned16(x) && aligned16(w);
+    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
     if (flags & LCE_FLAG_FORCE_TC) {
         if (flags & LCE_FLAG_FORCE_SIMT) return LCE_ERR_ARG;
         if (dtype == LCE_DTYPE_F32) return LCE_ERR_ARG;
@@ -278,9 +307,9 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     off += align_up(static_cast<size_t>(p.nr) * p.ldg * e, 256);
     p.off_dx_scratch = off;
     if (need_dx && p.n_cblk > 1)
-        off += align_up(static_cast<size_t>(cdiv(p.nr, kBM)) * cdiv(H, p.bn) * kBM * p.bn * sizeof(float), 256);
+        off += align_up(static_cast<size_t>(cdiv(p.nr, 2 * kBM) * 2) * cdiv(H, p.bn) * kBM * p.bn * sizeof(float), 256);
     p.off_dw_scratch = off;
-    p.dw_band_scratch_floats = cdiv(p.nc, kBM) * cdiv(H, p.bn) * kBM * p.bn;
+    p.dw_band_scratch_floats = cdiv(p.nc, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
     if (need_dw && p.n_rblk > 1)
         off += align_up(static_cast<size_t>(p.n_cblk) * p.dw_band_scratch_floats * sizeof(float), 256);
     p.total = off;
@@ -547,13 +576,14 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
 }
 
 int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,
-                   int a_mn, int b_mn, int dtype, void* stream) {
+                   int a_mn, int b_mn, int dtype, unsigned flags, void* stream) {
     if (!a || !b || !out || M <= 0 || N <= 0 || K <= 0) return LCE_ERR_ARG;
     if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16) return LCE_ERR_ARG;
     DeviceInfo* d;
     int rc = device_info(&d);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
     EpiStore<float>::Params ep;
     ep.out = out;
     ep.ldo = N;

@@ -126,6 +126,8 @@ def _path_flags() -> int:
         return _lib.FLAG_FORCE_SIMT
     if force == "tc":
         return _lib.FLAG_FORCE_TC
+    if force == "tc1":  # tensor-core path on single CTAs (cta_group::1) instead of CTA pairs
+        return _lib.FLAG_FORCE_TC | _lib.FLAG_ONE_CTA
     return 0
 
 
@@ -351,7 +353,8 @@ def linear_cross_entropy(
     return _LinearCrossEntropy.apply(hidden, weight, target, reduction, ignore_index, process_group, vocab_start)
 
 
-def debug_gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool, b_mn_major: bool) -> torch.Tensor:
+def debug_gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool, b_mn_major: bool,
+               one_cta: bool = False) -> torch.Tensor:
     """``A @ B.T`` in float32 on the tcgen05 GEMM core (test hook for the operand layouts)."""
     m, k = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
     n = b.shape[1] if b_mn_major else b.shape[0]
@@ -359,7 +362,8 @@ def debug_gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool, b_mn_major: b
     with torch.cuda.device(a.device):
         _lib.check(
             _lib.lib().lce_debug_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, int(a_mn_major),
-                                      int(b_mn_major), _DTYPE_CODE[a.dtype], _stream(a.device)),
+                                      int(b_mn_major), _DTYPE_CODE[a.dtype],
+                                      _lib.FLAG_ONE_CTA if one_cta else 0, _stream(a.device)),
             "lce_debug_gemm",
         )
     return out

@@ -47,6 +47,8 @@ extern "C" {
 #define LCE_FLAG_DX_F32 4u     /* dx is float32 [N, H]: a partial sum another rank will reduce   */
 #define LCE_FLAG_NO_DX 8u      /* skip dX (dx may be NULL)                                       */
 #define LCE_FLAG_NO_DW 16u     /* skip dW (dw may be NULL)                                       */
+#define LCE_FLAG_ONE_CTA 32u   /* tcgen05 cta_group::1 (one CTA per 128x256 tile) instead of the
+                                  default CTA pairs (cta_group::2, 256x256 tiles)                  */
 
 /* status codes */
 #define LCE_OK 0
@@ -145,7 +147,7 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
  * with N. No counterpart in the reference; exists so the operand-layout handling can be tested
  * in isolation. */
 int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,
-                   int a_mn_major, int b_mn_major, int dtype, void* stream);
+                   int a_mn_major, int b_mn_major, int dtype, unsigned flags, void* stream);
 
 #ifdef __cplusplus
 }

@@ -171,7 +171,7 @@ SCALED = [
 ]
 
 
-@pytest.mark.parametrize("force", ["tc", "simt"])
+@pytest.mark.parametrize("force", ["tc", "tc1", "simt"])
 @pytest.mark.parametrize("name,shape", SCALED, ids=[s[0] for s in SCALED])
 def test_scaled_configurations(name, shape, force, monkeypatch):
     monkeypatch.setenv("HELION_B200_FORCE", force)
@@ -261,7 +261,7 @@ def test_partial_needs_input_grad():
     assert torch.equal(x1.grad, xg.grad) and torch.equal(w1.grad, wg.grad)
 
 
-@pytest.mark.parametrize("force", ["tc", "simt"])
+@pytest.mark.parametrize("force", ["tc", "tc1", "simt"])
 def test_block_plans_agree_and_runs_are_bit_identical(force, monkeypatch):
     """Vocab bands, row chunks and the 2-D grid of blocks sum partial dX / dW in fp32 in a fixed order:
     every plan matches the single-block result to rounding, and the same plan twice is bit-identical."""
@@ -313,13 +313,15 @@ def test_both_kernel_families_agree():
 @pytest.mark.parametrize("a_mn", [False, True])
 @pytest.mark.parametrize("b_mn", [False, True])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_gemm_core_operand_layouts(a_mn, b_mn, dtype):
+@pytest.mark.parametrize("one_cta", [False, True], ids=["cta-pair", "one-cta"])
+def test_gemm_core_operand_layouts(a_mn, b_mn, dtype, one_cta):
     g = torch.Generator().manual_seed(15)
-    for m, n, k in [(128, 256, 64), (392, 520, 200), (136, 8, 72)]:
+    for m, n, k in [(128, 256, 64), (392, 520, 200), (136, 8, 72), (1304, 264, 136)]:
         a = torch.randn(m, k, generator=g).to(dtype)
         b = torch.randn(n, k, generator=g).to(dtype)
         ref = a.float() @ b.float().T
-        out = ops.debug_gemm((a.T.contiguous() if a_mn else a).to(DEV), (b.T.contiguous() if b_mn else b).to(DEV), a_mn, b_mn)
+        out = ops.debug_gemm((a.T.contiguous() if a_mn else a).to(DEV), (b.T.contiguous() if b_mn else b).to(DEV), a_mn, b_mn,
+                             one_cta=one_cta)
         assert scaled_max_err(out, ref) <= 1e-5
 
 
