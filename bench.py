@@ -19,7 +19,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -43,64 +42,71 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML every few milliseconds while the timed
+    region runs (read-only queries; nothing on the GPU is changed)."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.lines: list[str] = []
-        self.thread = None
+        self.period_s = period_s
+        self.samples: list[tuple[int, float, int]] = []
+        self.sm_max = None
+        self.error = None
+        self._stop = threading.Event()
+        self._thread = None
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
+            import pynvml
 
-    def _pump(self) -> None:
-        assert self.proc is not None and self.proc.stdout is not None
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.gpu_index]) if visible else self.gpu_index
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+            self.error = f"nvml unavailable: {exc}"
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                clock = nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)
+                power = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                self.samples.append((clock, power, reasons))
+            except Exception as exc:  # noqa: BLE001
+                self.error = str(exc)
+                return
+            time.sleep(self.period_s)
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-                power.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+        if self._thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": [self.error or "not started"]}
+        self._stop.set()
+        self._thread.join(timeout=2)
+        nv = self._nvml
+        names = {
+            "hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+            "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+            "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap,
+        }
+        seen = set()
+        for _, _, mask in self.samples:
+            for name, bit in names.items():
+                if mask & bit:
+                    seen.add(name)
+        clocks = [c for c, _, _ in self.samples]
         return {
-            "sm_mhz": statistics.median(sm) if sm else None,
-            "sm_max_mhz": max(smax) if smax else None,
-            "power_w_max": max(power) if power else None,
-            "samples": len(sm),
-            "reasons": sorted(reasons),
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": self.sm_max,
+            "power_w_max": max((p for _, p, _ in self.samples), default=None),
+            "samples": len(clocks),
+            "reasons": sorted(seen),
         }
 
 
@@ -167,8 +173,9 @@ def run_reference(args) -> None:
     cfg = build_workload(args.workload)
     data = inputs.make_inputs(cfg)
     flops_per_row = 8.0 * cfg.hidden * cfg.vocab
-    # about 2e12 FLOP of CPU work per step keeps a default run within a few minutes
-    sample_rows = max(16, min(cfg.rows, int(2.0e12 / flops_per_row)))
+    # at most 2e12 FLOP of CPU work per step and 1e14 FLOP per run: a couple of minutes on 16 cores
+    per_step = min(2.0e12, 1.0e14 / max(1, args.steps + min(args.warmup, 2)))
+    sample_rows = max(16, min(cfg.rows, int(per_step / flops_per_row)))
     base = cpu_baseline(data, sample_rows, repeats=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
     sec = base["seconds_per_sample"]
     line = {

@@ -325,7 +325,8 @@ int store_mode(long long idx, long long count) {
 template <class T, class TDx>
 int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void* x, const void* w,
                   const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
-                  long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, cudaStream_t stream) {
+                  long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, void* const* dx_events,
+                  cudaStream_t stream) {
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
     const T* xp = static_cast<const T*>(x);
     const T* wp = static_cast<const T*>(w);
@@ -364,26 +365,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 if (rc) return rc;
             }
             const Mat gm{g, nr, nc, p.ldg};
-            // ---- step 2: dW[c0 : c0+nc, :] (+)= G^T @ X[r0 : r0+nr, :]
-            if (need_dw) {
-                typename EpiStore<T>::Params ep;
-                ep.out = static_cast<T*>(dw) + c0 * H;
-                ep.ldo = H;
-                ep.rows = static_cast<int>(nc);
-                ep.cols = static_cast<int>(H);
-                ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
-                ep.mode = store_mode(rb, p.n_rblk);
-                const Mat b{xp + r0 * H, nr, H, H};
-                if (use_tc) {
-                    if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream);
-                    else rc = LCE_ERR_ARG;
-                } else {
-                    rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream);
-                }
-                if (rc) return rc;
-            }
-            // ---- step 3: dX[r0 : r0+nr, :] (+)= G @ W[c0 : c0+nc, :]
+            // ---- step 2: dX[r0 : r0+nr, :] (+)= G @ W[c0 : c0+nc, :]
             if (need_dx) {
                 typename EpiStore<TDx>::Params ep;
                 ep.out = static_cast<TDx*>(dx) + r0 * H;
@@ -399,6 +381,30 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream);
+                }
+                if (rc) return rc;
+                // rows r0.. of dX are final after the last band: let the caller start reducing them
+                // while the dW GEMM below (and later chunks) still run
+                if (dx_events && cb == p.n_cblk - 1 && dx_events[rb] &&
+                    cudaEventRecord(static_cast<cudaEvent_t>(dx_events[rb]), stream) != cudaSuccess)
+                    return LCE_ERR_CUDA;
+            }
+            // ---- step 3: dW[c0 : c0+nc, :] (+)= G^T @ X[r0 : r0+nr, :]
+            if (need_dw) {
+                typename EpiStore<T>::Params ep;
+                ep.out = static_cast<T*>(dw) + c0 * H;
+                ep.ldo = H;
+                ep.rows = static_cast<int>(nc);
+                ep.cols = static_cast<int>(H);
+                ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
+                ep.mode = store_mode(rb, p.n_rblk);
+                const Mat b{xp + r0 * H, nr, H, H};
+                if (use_tc) {
+                    if constexpr (sizeof(T) == 2)
+                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream);
+                    else rc = LCE_ERR_ARG;
+                } else {
+                    rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream);
                 }
                 if (rc) return rc;
             }
@@ -523,10 +529,25 @@ size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, 
     return a > b ? a : b;
 }
 
+int lce_backward_plan(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags, size_t block_bytes,
+                      const void* x, const void* w, int64_t* out) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (!out) return LCE_ERR_ARG;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    const BwdPlan p = plan_backward(N, H, V, dtype, use_tc, flags, block_bytes);
+    out[0] = p.nr;
+    out[1] = p.nc;
+    out[2] = p.n_rblk;
+    out[3] = p.n_cblk;
+    return LCE_OK;
+}
+
 int lce_backward(const void* x, const void* w, const void* target, int target_is_i64, const float* lse,
                  const float* grad_out, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
                  int64_t ignore_index, int reduction, void* dx, void* dw, void* ws, size_t ws_bytes,
-                 unsigned flags, size_t block_bytes, void* stream) {
+                 unsigned flags, size_t block_bytes, void* const* dx_events, void* stream) {
     int rc = check_dims(N, H, V, dtype);
     if (rc) return rc;
     if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
@@ -564,9 +585,9 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
 #define LCE_BWD(T)                                                                                          \
     (dx32 ? backward_impl<T, float>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
-                                    dx, dw, wsc, flags, s)                                                  \
+                                    dx, dw, wsc, flags, dx_events, s)                                       \
           : backward_impl<T, T>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
-                                dw, wsc, flags, s))
+                                dw, wsc, flags, dx_events, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
         case LCE_DTYPE_F16: return LCE_BWD(__half);

@@ -16,6 +16,7 @@ All GPU work happens in libhelion_lce.so; nothing here computes on the CPU or th
 
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Any
 
@@ -254,18 +255,30 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     grad_out = grad_out.contiguous()
     dtype = _DTYPE_CODE[hidden2d.dtype]
     block = _block_bytes()
+    vstart = _resolve_vocab_start(vocab_start, rank, v_local)
     ws = _workspace(L.lce_backward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags, block), dev)
+
+    # Sharded: the partial dX of each row chunk is summed over the group on a side stream as soon as
+    # the library signals that chunk final, while the remaining dW GEMMs run on the main stream.
+    events, event_array, chunk_rows = None, None, n_rows
+    if sharded and dx is not None:
+        plan = (ctypes.c_int64 * 4)()
+        _lib.check(L.lce_backward_plan(n_rows, hidden_size, v_local, dtype, flags, block, hidden2d.data_ptr(),
+                                       weight.data_ptr(), plan), "lce_backward_plan")
+        chunk_rows, n_chunks = int(plan[0]), int(plan[2])
+        events = parallel.ready_events(dev, n_chunks)
+        event_array = (ctypes.c_void_p * n_chunks)(*[e.cuda_event for e in events])
+
     with torch.cuda.device(dev):
         _lib.check(
             L.lce_backward(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
                            int(target1d.dtype == torch.int64), logsumexp.data_ptr(), grad_out.data_ptr(), n_rows,
-                           hidden_size, v_local, _resolve_vocab_start(vocab_start, rank, v_local), dtype,
-                           ignore_index, red, _ptr(dx), _ptr(dw), ws.data_ptr(), ws.numel(), flags, block,
-                           _stream(dev)),
+                           hidden_size, v_local, vstart, dtype, ignore_index, red, _ptr(dx), _ptr(dw), ws.data_ptr(),
+                           ws.numel(), flags, block, event_array, _stream(dev)),
             "lce_backward",
         )
     if sharded and dx is not None:
-        dx = parallel.reduce_dx(dx, hidden2d.dtype, process_group)
+        dx = parallel.reduce_dx_chunks(dx, chunk_rows, events, hidden2d.dtype, process_group)
     return dx, dw
 
 

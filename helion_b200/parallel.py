@@ -62,3 +62,48 @@ def reduce_dx(dx_partial: torch.Tensor, out_dtype: torch.dtype, process_group: A
 
         dist.all_reduce(dx_partial, op=dist.ReduceOp.SUM, group=process_group)
     return dx_partial if dx_partial.dtype == out_dtype else dx_partial.to(out_dtype)
+
+
+# ---- overlap of the dX reduction with the rest of the backward pass ---------------------------------
+_comm_streams: dict[int, "torch.cuda.Stream"] = {}
+_event_pool: dict[int, list["torch.cuda.Event"]] = {}
+
+
+def comm_stream(device: torch.device) -> "torch.cuda.Stream":
+    """The side stream (one per device) on which partial dX is reduced."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _comm_streams:
+        _comm_streams[idx] = torch.cuda.Stream(device=device)
+    return _comm_streams[idx]
+
+
+def ready_events(device: torch.device, count: int) -> list["torch.cuda.Event"]:
+    """``count`` reusable CUDA events whose raw handles the C ABI may record.
+
+    torch creates an event lazily on its first ``record``; each event is recorded once here so that
+    ``cuda_event`` is a real handle before it crosses the C ABI."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    pool = _event_pool.setdefault(idx, [])
+    while len(pool) < count:
+        ev = torch.cuda.Event(enable_timing=False)
+        ev.record(torch.cuda.current_stream(device))
+        pool.append(ev)
+    return pool[:count]
+
+
+def reduce_dx_chunks(dx_partial: torch.Tensor, chunk_rows: int, events, out_dtype: torch.dtype,
+                     process_group: Any) -> torch.Tensor:
+    """All-reduce ``dx_partial`` row chunk by row chunk on the side stream, each chunk as soon as its
+    event fires; the calling stream then waits for the side stream and rounds once to ``out_dtype``."""
+    import torch.distributed as dist
+
+    dev = dx_partial.device
+    main = torch.cuda.current_stream(dev)
+    side = comm_stream(dev)
+    for i, ev in enumerate(events):
+        side.wait_event(ev)
+        with torch.cuda.stream(side):
+            dist.all_reduce(dx_partial[i * chunk_rows:(i + 1) * chunk_rows], op=dist.ReduceOp.SUM,
+                            group=process_group)
+    main.wait_stream(side)
+    return dx_partial if dx_partial.dtype == out_dtype else dx_partial.to(out_dtype)

@@ -132,14 +132,24 @@ int lce_finalize(const float* stats, int R, const void* target, int target_is_i6
  *   dw = G^T @ x  [V_local, H]  (input dtype)
  * grad_out is read on the device: one float for MEAN / SUM, N floats for NONE.
  * G is staged block by block through `ws` (block_bytes caps one block; 0 = default 256 MiB), and
- * partial sums over blocks are added in a fixed order in fp32, so results are deterministic. */
+ * partial sums over blocks are added in a fixed order in fp32, so results are deterministic.
+ * dx_events: NULL, or one cudaEvent_t per row chunk of lce_backward_plan(); event i is recorded on
+ * `stream` as soon as the dx rows of chunk i are final (before the remaining dW work), so that a
+ * caller can start reducing partial dx across ranks on another stream while this call's GEMMs run. */
 size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
                                     size_t block_bytes);
 int lce_backward(const void* x, const void* w, const void* target, int target_is_i64,
                  const float* lse, const float* grad_out, int64_t N, int64_t H, int64_t V_local,
                  int64_t vocab_start, int dtype, int64_t ignore_index, int reduction, void* dx,
                  void* dw, void* ws, size_t ws_bytes, unsigned flags, size_t block_bytes,
-                 void* stream);
+                 void* const* dx_events, void* stream);
+
+/* The block grid lce_backward will use for these arguments (x and w only decide, by their
+ * alignment, which kernel family runs): out[0] = rows per row chunk, out[1] = vocabulary columns per
+ * band, out[2] = number of row chunks, out[3] = number of bands. Host-only. No counterpart in the
+ * reference (its chunk size is _linear_ce_backward_chunk_size, tritium/ops/cross_entropy.py:515-519). */
+int lce_backward_plan(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
+                      size_t block_bytes, const void* x, const void* w, int64_t* out);
 
 /* ---- test hook -------------------------------------------------------------------------------
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
