@@ -32,6 +32,9 @@ SIGNATURES = {
     "lce_finalize_workspace_bytes": (c_size_t, [c_int64]),
     "lce_finalize": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lce_forward_loss_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
+    "lce_forward_loss": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int64,
+                                 c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
     "lce_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t]),
     "lce_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t,

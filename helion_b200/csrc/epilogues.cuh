@@ -197,12 +197,16 @@ struct EpiGrad {
 //   kStoreFirst   scratch = acc                  (first partial sum)
 //   kStoreAccum   scratch += acc
 //   kStoreLast    out = scratch + acc            (rounded to the output dtype once, at the end)
+//   kStoreSlice   scratch[k_slice] = acc         (split-K inside one launch: each slice of the
+//                                                 contraction writes its own slab of slab_floats
+//                                                 floats; splitk_reduce_kernel adds the slabs in
+//                                                 slice order afterwards)
 // The launches of one sum run in stream order, so the summation order - and the result - is the
 // same on every run (this is the deterministic split-K). The scratch buffer is private to the
 // library, so it is laid out for coalescing, not as a matrix: float4 index
 //   ((tile * bn/4 + col/4) * 128 + row_in_tile).
 // ---------------------------------------------------------------------------------------------
-enum StoreMode { kStoreDirect = 0, kStoreFirst = 1, kStoreAccum = 2, kStoreLast = 3 };
+enum StoreMode { kStoreDirect = 0, kStoreFirst = 1, kStoreAccum = 2, kStoreLast = 3, kStoreSlice = 4 };
 
 template <class T>
 struct EpiStore {
@@ -212,6 +216,7 @@ struct EpiStore {
         int rows, cols;  // valid extent of the output block
         float* scratch;
         int mode;
+        long long slab_floats;  // kStoreSlice: distance between the slabs of consecutive k slices
     };
     struct State {
         int row;
@@ -226,7 +231,8 @@ struct EpiStore {
             float4* sp = reinterpret_cast<float4*>(p.scratch) +
                          ((static_cast<long long>(tc.m_tile) * tc.n_tiles + tc.n_tile) * (tc.bn / 4) +
                           col0 / 4) * kBM + tc.row_in_tile;
-            if (p.mode != kStoreFirst) {
+            if (p.mode == kStoreSlice) sp += static_cast<long long>(tc.k_slice) * (p.slab_floats / 4);
+            if (p.mode != kStoreFirst && p.mode != kStoreSlice) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 o = sp[i * kBM];

@@ -54,6 +54,7 @@ struct TileCtx {
     int n_tiles;      // tile columns in the problem
     int row_in_tile;  // 0..127, the row this thread owns
     int bn;           // tile width in columns
+    int k_slice;      // which slice of the contraction this tile holds (0 unless K is split)
 };
 
 template <int BN, int STAGES, int CG>
@@ -83,10 +84,14 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 // m_tiles counts 128-row tiles. With CG = 2 the scheduler deals out pairs of them: unit u covers
 // m tiles 2u and 2u+1 (the second may lie past the end of the matrix: its loads return zeros
 // and the epilogues skip its rows).
+// k_splits > 1 splits the contraction: work item w = (tile unit w % units, slice w / units) covers
+// k blocks [slice * per, (slice+1) * per) and hands the epilogue a partial sum tagged with its slice
+// (the epilogue stores slices side by side; a later pass adds them in slice order). The host
+// guarantees that every slice is non-empty.
 template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               int m_tiles, int n_tiles, int k_blocks, int m_fastest,
+               int m_tiles, int n_tiles, int k_blocks, int k_splits, int m_fastest,
                const typename Epi::Params ep, int* __restrict__ status) {
     using S = GemmSmem<BN, STAGES, CG>;
     static_assert(CG == 1 || CG == 2, "cta group");
@@ -118,6 +123,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int unit_step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     const int m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
     const int total_units = m_units * n_tiles;
+    const int total_work = total_units * k_splits;
+    const int kb_per_slice = (k_blocks + k_splits - 1) / k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -155,12 +162,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t issued = 0;
             bool ok = true;
             const uint32_t leader_full0 = kPair ? ptx::map_to_cta(full_bar(0), 0) : 0u;
-            for (int unit = unit0; unit < total_units && ok; unit += unit_step) {
+            for (int work = unit0; work < total_work && ok; work += unit_step) {
                 int m_unit, n_tile;
-                tile_coords(unit, m_units, n_tiles, m_fastest, m_unit, n_tile);
+                tile_coords(work % total_units, m_units, n_tiles, m_fastest, m_unit, n_tile);
+                const int kb_begin = (work / total_units) * kb_per_slice;
+                const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
                 const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
                 const int b_row0 = n_tile * BN + static_cast<int>(cta_rank) * S::kBRows;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const uint32_t stage = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1u;
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -220,7 +229,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t consumed = 0;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int unit = unit0; unit < total_units && ok; unit += unit_step, ++local_tile) {
+            for (int work = unit0; work < total_work && ok; work += unit_step, ++local_tile) {
+                const int kb_begin = (work / total_units) * kb_per_slice;
+                const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
                 const uint32_t buf = local_tile & 1u;
                 const uint32_t buf_phase = (local_tile >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty_bar(buf), buf_phase ^ 1u, abort_flag)) {
@@ -229,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const uint32_t stage = consumed % STAGES;
                     const uint32_t phase = (consumed / STAGES) & 1u;
                     if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
@@ -249,8 +260,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const uint64_t db =
                             B_MN ? ptx::make_smem_desc(sb + k * (kUmmaK * 128), kBK * 128, 1024)
                                  : ptx::make_smem_desc(sb + k * (kUmmaK * 2), 0, 1024);
-                        if constexpr (kPair) ptx::umma_f16_pair(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
-                        else ptx::umma_f16(tmem_d, da, db, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        const uint32_t acc = (kb != kb_begin || k != 0) ? 1u : 0u;  // first MMA of a tile overwrites
+                        if constexpr (kPair) ptx::umma_f16_pair(tmem_d, da, db, kIdesc, acc);
+                        else ptx::umma_f16(tmem_d, da, db, kIdesc, acc);
                     }
                     // smem slot reusable (in both CTAs of a pair) once these MMAs retire
                     if constexpr (kPair) ptx::umma_commit_pair(empty_bar(stage), 3);
@@ -277,13 +289,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t local_tile = 0;
         bool ok = true;
         typename Epi::State st;
-        for (int unit = unit0; unit < total_units && ok; unit += unit_step, ++local_tile) {
+        for (int work = unit0; work < total_work && ok; work += unit_step, ++local_tile) {
             int m_unit, n_tile;
-            tile_coords(unit, m_units, n_tiles, m_fastest, m_unit, n_tile);
+            tile_coords(work % total_units, m_units, n_tiles, m_fastest, m_unit, n_tile);
             const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
             const uint32_t buf = local_tile & 1u;
             const uint32_t buf_phase = (local_tile >> 1) & 1u;
-            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN};
+            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN, work / total_units};
             Epi::begin(st, ep, tc);  // global loads for this row overlap the wait below
             if (!ptx::mbar_wait(tfull_bar(buf), buf_phase, abort_flag)) {
                 ok = false;

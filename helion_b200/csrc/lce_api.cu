@@ -26,6 +26,7 @@ constexpr int kMaxDevices = 64;
 
 struct DeviceInfo {
     bool ready = false;
+    int index = 0;
     int sm_count = 0;
     int cc_major = 0;
     int* status_ptr = nullptr;
@@ -46,6 +47,7 @@ int device_info(DeviceInfo** out) {
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceInfo& d = g_dev[dev];
     if (!d.ready) {
+        d.index = dev;
         if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
             return LCE_ERR_CUDA;
         if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
@@ -99,7 +101,7 @@ struct Mat {
 
 template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-                 int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
+                 int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream) {
     constexpr int kStages = CG == 2 ? kStages2 : kStages1;
     const int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
     CUtensorMap tma, tmb;
@@ -115,12 +117,19 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     const long long units = cdiv(m_tiles, CG) * n_tiles;
     if (m_tiles * n_tiles > 0x3fffffffll || k_blocks > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
     if (units == 0 || k_blocks == 0) return LCE_OK;
+    // every k slice must hold at least one block
+    if (k_splits < 1 || (k_splits - 1) * cdiv(k_blocks, k_splits) >= k_blocks) return LCE_ERR_ARG;
     auto kern = gemm_tc_kernel<kBN, kStages, CG, A_MN, B_MN, IS_BF16, Epi>;
     constexpr int smem = GemmSmem<kBN, kStages, CG>::kTotalBytes;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return LCE_ERR_CUDA;
+    static bool smem_opted_in[kMaxDevices] = {};  // per kernel instantiation and device
+    if (!smem_opted_in[d.index]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return LCE_ERR_CUDA;
+        smem_opted_in[d.index] = true;
+    }
     const long long slots = d.sm_count / CG;  // one CTA per SM; a pair occupies the two SMs of a TPC
-    const int grid = static_cast<int>(units < slots ? units : slots) * CG;
+    const long long work = units * k_splits;
+    const int grid = static_cast<int>(work < slots ? work : slots) * CG;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kGemmThreads);
@@ -134,18 +143,39 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     cfg.attrs = attr;
     cfg.numAttrs = CG > 1 ? 1 : 0;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
-                                               static_cast<int>(n_tiles), static_cast<int>(k_blocks), m_fastest,
-                                               ep, d.status_ptr);
+                                               static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
+                                               m_fastest, ep, d.status_ptr);
     LCE_COUNT_LAUNCH();
     return err == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
+// CTA pairs cover two 128-row tiles at a time; with an odd, small number of row tiles the second
+// half of the last pair would idle, so such problems run on single CTAs.
+bool use_pair(long long M) {
+    const long long m_tiles = cdiv(M, kBM);
+    return t_cta_group == 2 && (m_tiles % 2 == 0 || m_tiles >= 16);
+}
+
 template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream) {
-    if (t_cta_group == 2)
-        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, ep, stream);
-    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, ep, stream);
+              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1) {
+    if (use_pair(M))
+        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
+    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
+}
+
+// How many slices to cut the contraction of an M x Nn x K GEMM into so that a problem with few output
+// tiles still fills the GPU (the deterministic split-K: slices are added in slice order afterwards).
+// Uses a fixed SM count so that workspace sizes do not depend on the device.
+int choose_k_splits(long long M, long long Nn, long long K) {
+    const long long slots = use_pair(M) ? 74 : 148;
+    const long long units = cdiv(cdiv(M, kBM), use_pair(M) ? 2 : 1) * cdiv(Nn, kBN);
+    const long long k_blocks = cdiv(K, kBK);
+    if (units == 0 || units * 2 > slots) return 1;
+    long long s = slots / units;
+    if (s > 16) s = 16;
+    while (s > 1 && (k_blocks / s < 8 || (s - 1) * cdiv(k_blocks, s) >= k_blocks)) --s;
+    return static_cast<int>(s);
 }
 
 template <class T, class Epi>
@@ -210,10 +240,19 @@ FwdLayout fwd_layout(long long N, long long V, bool use_tc) {
     return l;
 }
 
+// What follows the logits GEMM: either the merged statistics of this shard (for a cross-shard merge)
+// or, when the shard is the whole vocabulary, logsumexp and per-row loss straight away.
+struct FwdOutputs {
+    float* stats = nullptr;      // [3][N]
+    float* lse = nullptr;        // [N]       (fused finalize)
+    float* loss_rows = nullptr;  // [N]       (fused finalize)
+    long long ignore_index = -100;
+};
+
 template <class T>
 int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const void* w, const void* tgt,
                        int tgt_i64, long long N, long long H, long long V, long long vocab_start,
-                       float* stats, void* ws, cudaStream_t stream) {
+                       const FwdOutputs& out, void* ws, cudaStream_t stream) {
     const FwdLayout l = fwd_layout(N, V, use_tc);
     EpiStats::Params ep;
     ep.tgt = tgt;
@@ -236,8 +275,15 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
         rc = launch_simt<T, EpiStats>(d, a, false, b, false, N, V, H, ep, stream);
     }
     if (rc) return rc;
-    merge_partials_kernel<<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, stream>>>(
-        static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), stats);
+    const int blocks = static_cast<int>(cdiv(N, kMergeRows)), threads = kMergeRows * kMergeLanes;
+    if (out.stats != nullptr)
+        merge_partials_kernel<false><<<blocks, threads, 0, stream>>>(
+            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
+            out.stats, nullptr, 0, 0, nullptr, nullptr);
+    else
+        merge_partials_kernel<true><<<blocks, threads, 0, stream>>>(
+            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
+            nullptr, tgt, tgt_i64, out.ignore_index, out.lse, out.loss_rows);
     LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
@@ -257,6 +303,8 @@ struct BwdPlan {
     long long bn;              // tile width of the dX / dW GEMMs (for the scratch layout)
     size_t off_count, off_rowscale, off_g, off_dx_scratch, off_dw_scratch, total;
     long long dw_band_scratch_floats;
+    int dx_splits;               // k slices of the dX GEMM when one band covers the vocabulary
+    long long dx_slab_floats;    // fp32 scratch of one dX row chunk (one slice)
 };
 
 BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use_tc, unsigned flags,
@@ -306,8 +354,10 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     p.off_g = off;
     off += align_up(static_cast<size_t>(p.nr) * p.ldg * e, 256);
     p.off_dx_scratch = off;
-    if (need_dx && p.n_cblk > 1)
-        off += align_up(static_cast<size_t>(cdiv(p.nr, 2 * kBM) * 2) * cdiv(H, p.bn) * kBM * p.bn * sizeof(float), 256);
+    p.dx_slab_floats = cdiv(p.nr, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
+    p.dx_splits = (use_tc && need_dx && p.n_cblk == 1) ? choose_k_splits(p.nr, H, p.nc) : 1;
+    if (need_dx && (p.n_cblk > 1 || p.dx_splits > 1))
+        off += align_up(static_cast<size_t>(p.dx_splits) * p.dx_slab_floats * sizeof(float), 256);
     p.off_dw_scratch = off;
     p.dw_band_scratch_floats = cdiv(p.nc, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
     if (need_dw && p.n_rblk > 1)
@@ -374,15 +424,29 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 ep.cols = static_cast<int>(H);
                 ep.scratch = reinterpret_cast<float*>(ws + p.off_dx_scratch);
                 ep.mode = store_mode(cb, p.n_cblk);
+                ep.slab_floats = p.dx_slab_floats;
                 const Mat b{wp + c0 * H, nc, H, H};
+                // few output tiles (short row chunk): cut the vocabulary contraction into slices
+                const int splits = (p.dx_splits > 1 && nr == p.nr) ? p.dx_splits : 1;
+                if (splits > 1) ep.mode = kStoreSlice;
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, gm, b, nr, H, nc, 0, ep, stream);
+                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, gm, b, nr, H, nc, 0, ep, stream, splits);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream);
                 }
                 if (rc) return rc;
+                if (splits > 1) {
+                    const int m_tiles = static_cast<int>(cdiv(nr, kBM)), n_tiles = static_cast<int>(cdiv(H, kBN));
+                    const long long quads = static_cast<long long>(m_tiles) * n_tiles * (kBN / 4) * kBM;
+                    const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
+                    splitk_reduce_kernel<TDx><<<blocks, 256, 0, stream>>>(
+                        ep.scratch, splits, p.dx_slab_floats, m_tiles, n_tiles, kBN, static_cast<int>(nr),
+                        static_cast<int>(H), ep.out, H);
+                    LCE_COUNT_LAUNCH();
+                    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+                }
                 // rows r0.. of dX are final after the last band: let the caller start reducing them
                 // while the dW GEMM below (and later chunks) still run
                 if (dx_events && cb == p.n_cblk - 1 && dx_events[rb] &&
@@ -398,6 +462,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 ep.cols = static_cast<int>(H);
                 ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
                 ep.mode = store_mode(rb, p.n_rblk);
+                ep.slab_floats = 0;
                 const Mat b{xp + r0 * H, nr, H, H};
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
@@ -474,13 +539,15 @@ int lce_forward_stats(const void* x, const void* w, const void* target, int targ
     if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
     if (ws_bytes < fwd_layout(N, V, use_tc).bytes) return LCE_ERR_WS_TOO_SMALL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FwdOutputs fo;
+    fo.stats = stats;
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         case LCE_DTYPE_F16:
-            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         default:
-            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, ws, s);
+            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
     }
 }
 
@@ -520,9 +587,56 @@ int lce_finalize(const float* stats, int R, const void* target, int target_is_i6
     return LCE_OK;
 }
 
+size_t lce_forward_loss_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags) {
+    const size_t partial = lce_forward_workspace_bytes(N, H, V, dtype, flags);
+    return partial ? partial + lce_finalize_workspace_bytes(N) : 0;
+}
+
+int lce_forward_loss(const void* x, const void* w, const void* target, int target_is_i64, int64_t N, int64_t H,
+                     int64_t V, int dtype, int64_t ignore_index, int reduction, float* lse, float* loss,
+                     float* valid_count, void* ws, size_t ws_bytes, unsigned flags, void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
+        return LCE_ERR_ARG;
+    if (N == 0) return LCE_ERR_ARG;  // the empty batch is the caller's business (zero loss, no launch)
+    if (!x || !w || !target || !lse || !loss || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    const size_t partial_bytes = align_up(fwd_layout(N, V, use_tc).bytes, 256);
+    if (ws_bytes < partial_bytes + static_cast<size_t>(N) * sizeof(float)) return LCE_ERR_WS_TOO_SMALL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FwdOutputs fo;
+    fo.lse = lse;
+    fo.loss_rows = reduction == LCE_REDUCTION_NONE ? loss : reinterpret_cast<float*>(static_cast<char*>(ws) + partial_bytes);
+    fo.ignore_index = ignore_index;
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            rc = forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            break;
+        case LCE_DTYPE_F16:
+            rc = forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            break;
+        default:
+            rc = forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+    }
+    if (rc) return rc;
+    if (reduction != LCE_REDUCTION_NONE || valid_count) {
+        reduce_loss_kernel<<<1, 1024, 0, s>>>(fo.loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
+                                              reduction == LCE_REDUCTION_MEAN ? 1 : 0,
+                                              reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    return LCE_OK;
+}
+
 size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags,
                                     size_t block_bytes) {
     if (check_dims(N, H, V, dtype)) return 0;
+    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
     // the SIMT and tcgen05 plans differ only in scratch tiling; report the larger of the two
     const size_t a = plan_backward(N, H, V, dtype, true, flags, block_bytes).total;
     const size_t b = plan_backward(N, H, V, dtype, false, flags, block_bytes).total;
@@ -572,14 +686,17 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     char* wsc = static_cast<char*>(ws);
     float* count = reinterpret_cast<float*>(wsc + p.off_count);
     float* rowscale = reinterpret_cast<float*>(wsc + p.off_rowscale);
-    if (reduction == LCE_REDUCTION_MEAN) {
+    // small batches count their valid rows inside the rowscale launch; large ones in a launch of its own
+    const bool separate_count = reduction == LCE_REDUCTION_MEAN && N > 16384;
+    if (separate_count) {
         count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
         LCE_COUNT_LAUNCH();
         if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     }
     rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
         target, target_is_i64, static_cast<int>(N), ignore_index, grad_out,
-        reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0, count, rowscale);
+        reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0,
+        separate_count ? count : nullptr, rowscale);
     LCE_COUNT_LAUNCH();
     if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
@@ -612,6 +729,7 @@ int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t 
     ep.cols = static_cast<int>(N);
     ep.scratch = nullptr;
     ep.mode = kStoreDirect;
+    ep.slab_floats = 0;
     const Mat am = a_mn ? Mat{a, K, M, M} : Mat{a, M, K, K};
     const Mat bm = b_mn ? Mat{b, K, N, N} : Mat{b, N, K, K};
 #define LCE_DBG(AMN, BMN)                                                                               \
@@ -677,15 +795,17 @@ int lce_forward_stats_static(const void* x, const void* w, const void* target, i
     void* scratch = nullptr;
     if ((rc = static_scratch_address(&scratch))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FwdOutputs fo;
+    fo.stats = stats;
     // Nothing in the scratch has to start at zero: the GEMM epilogue writes every (tile, row) entry
     // the merge kernel reads, earlier in this same call and on the same stream.
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
         case LCE_DTYPE_F16:
-            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
         default:
-            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, stats, scratch, s);
+            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
     }
 }
 

@@ -20,9 +20,14 @@ __device__ __forceinline__ void merge_ms(float& m, float& s, float bm, float bs)
 constexpr int kMergeRows = 32;
 constexpr int kMergeLanes = 32;
 
+// FINALIZE = false: writes the merged statistics (stats [3][N]) for a later cross-shard merge.
+// FINALIZE = true: this shard is the whole vocabulary, so logsumexp and the per-row loss are
+// written directly (lse[N], loss_rows[N]; 0 for ignored rows) and the statistics never reach memory.
+template <bool FINALIZE>
 __global__ void __launch_bounds__(kMergeRows * kMergeLanes)
 merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N,
-                      float* __restrict__ stats) {
+                      float* __restrict__ stats, const void* tgt, int tgt_i64, long long ignore_index,
+                      float* __restrict__ lse, float* __restrict__ loss_rows) {
     __shared__ float sm[kMergeLanes][kMergeRows + 1], ss[kMergeLanes][kMergeRows + 1],
         st[kMergeLanes][kMergeRows + 1];
     const int r = threadIdx.x % kMergeRows;
@@ -45,9 +50,15 @@ merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long 
             merge_ms(m, s, sm[k][r], ss[k][r]);
             t = fmaxf(t, st[k][r]);
         }
-        stats[row] = m;
-        stats[static_cast<long long>(N) + row] = s;
-        stats[2ll * N + row] = t;
+        if constexpr (FINALIZE) {
+            const float l = m + logf(s);
+            lse[row] = l;
+            loss_rows[row] = (load_target(tgt, tgt_i64, row) != ignore_index) ? (l - t) : 0.f;
+        } else {
+            stats[row] = m;
+            stats[static_cast<long long>(N) + row] = s;
+            stats[2ll * N + row] = t;
+        }
     }
 }
 
@@ -119,16 +130,75 @@ count_valid_kernel(const void* tgt, int tgt_i64, int N, long long ignore_index,
 }
 
 // rowscale[i] = upstream gradient factor of row i (0 for ignored rows); grad_out stays on device.
-__global__ void rowscale_kernel(const void* tgt, int tgt_i64, int N, long long ignore_index,
-                                const float* __restrict__ grad_out, int per_row, int mean,
-                                const float* __restrict__ valid_count,
-                                float* __restrict__ rowscale) {
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+// valid_count == nullptr (small N): every CTA counts the valid rows itself instead of waiting for a
+// separate counting launch; the count is an integer below 2^24, so any summation order is exact.
+__global__ void __launch_bounds__(256)
+rowscale_kernel(const void* tgt, int tgt_i64, int N, long long ignore_index,
+                const float* __restrict__ grad_out, int per_row, int mean,
+                const float* __restrict__ valid_count, float* __restrict__ rowscale) {
+    __shared__ int warp_counts[8];
+    __shared__ float count_sh;
+    float count = 1.f;
+    if (mean) {
+        if (valid_count != nullptr) {
+            count = *valid_count;
+        } else {
+            int c = 0;
+            for (int i = threadIdx.x; i < N; i += 256) c += load_target(tgt, tgt_i64, i) != ignore_index;
+            c = __reduce_add_sync(0xffffffffu, c);
+            if ((threadIdx.x & 31) == 0) warp_counts[threadIdx.x >> 5] = c;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int total = 0;
+                for (int k = 0; k < 8; ++k) total += warp_counts[k];
+                count_sh = static_cast<float>(total);
+            }
+            __syncthreads();
+            count = count_sh;
+        }
+    }
+    const int row = blockIdx.x * 256 + threadIdx.x;
     if (row >= N) return;
     const bool valid = load_target(tgt, tgt_i64, row) != ignore_index;
     float g = per_row ? grad_out[row] : grad_out[0];
-    if (mean) g = g / *valid_count;
+    if (mean) g = g / count;
     rowscale[row] = valid ? g : 0.f;
+}
+
+// Adds the `slices` slabs a split-K launch left in tile-blocked scratch (see EpiStore) in slice order
+// and writes the [rows, cols] result row-major. One thread per (tile, column quad, row): reads are
+// 16-byte coalesced along the rows of a tile.
+template <class T>
+__global__ void splitk_reduce_kernel(const float* __restrict__ scratch, int slices, long long slab_floats,
+                                     int m_tiles, int n_tiles, int bn, int rows, int cols,
+                                     T* __restrict__ out, long long ldo) {
+    const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
+    for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < quads;
+         q += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row_in_tile = static_cast<int>(q % kBM);
+        const long long rest = q / kBM;
+        const int c4 = static_cast<int>(rest % (bn / 4));
+        const long long tile = rest / (bn / 4);
+        const int n_tile = static_cast<int>(tile % n_tiles);
+        const int m_tile = static_cast<int>(tile / n_tiles);
+        const int row = m_tile * kBM + row_in_tile;
+        const int col = n_tile * bn + c4 * 4;
+        if (row >= rows || col >= cols) continue;
+        const float4* sp = reinterpret_cast<const float4*>(scratch) + q;
+        float4 acc = sp[0];
+        for (int s = 1; s < slices; ++s) {
+            const float4 v = sp[static_cast<long long>(s) * (slab_floats / 4)];
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        T* dst = out + static_cast<long long>(row) * ldo + col;
+        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (col + j < cols) dst[j] = Cvt<T>::from_f(vals[j]);
+    }
 }
 
 }  // namespace lce

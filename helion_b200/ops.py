@@ -137,7 +137,31 @@ def _block_bytes() -> int:
 
 
 def _stream(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw handle of torch's current stream on ``device`` (the stream every launch is enqueued on)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(device.index if device.index is not None else
+                                                  torch.cuda.current_device())
+    except AttributeError:  # older / newer torch without the private fast path
+        return torch.cuda.current_stream(device).cuda_stream
+
+
+class _on_device:
+    """Makes ``device`` current for the duration of a C-ABI call, at no cost when it already is."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device: torch.device):
+        self.guard = None
+        if device.index is not None and device.index != torch.cuda.current_device():
+            self.guard = torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -166,7 +190,7 @@ def local_stats(hidden2d: torch.Tensor, weight: torch.Tensor, target1d: torch.Te
     stats = torch.empty((3, n_rows), dtype=torch.float32, device=dev)
     dtype = _DTYPE_CODE[hidden2d.dtype]
     ws = _workspace(L.lce_forward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags), dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(
             L.lce_forward_stats(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
                                 int(target1d.dtype == torch.int64), n_rows, hidden_size, v_local, vocab_start,
@@ -187,7 +211,7 @@ def finalize(stats: torch.Tensor, target1d: torch.Tensor, reduction: str, ignore
     loss = torch.empty((n_rows,) if red == _lib.REDUCTION_NONE else (), dtype=torch.float32, device=dev)
     count = torch.empty((), dtype=torch.float32, device=dev) if want_count else None
     ws = _workspace(L.lce_finalize_workspace_bytes(n_rows), dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(
             L.lce_finalize(stats.data_ptr(), n_shards, target1d.data_ptr(), int(target1d.dtype == torch.int64),
                            n_rows, ignore_index, red, lse.data_ptr(), loss.data_ptr(), _ptr(count),
@@ -195,6 +219,28 @@ def finalize(stats: torch.Tensor, target1d: torch.Tensor, reduction: str, ignore
             "lce_finalize",
         )
     return loss, lse, count
+
+
+def _forward_single(hidden2d: torch.Tensor, weight: torch.Tensor, target1d: torch.Tensor, target_shape,
+                    red: int, ignore_index: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Unsharded forward in one C-ABI call (GEMM + statistics, fused merge/finalize, loss reduction)."""
+    n_rows, hidden_size = hidden2d.shape
+    v = weight.shape[0]
+    dev = hidden2d.device
+    L = _lib.lib()
+    dtype = _DTYPE_CODE[hidden2d.dtype]
+    flags = _path_flags()
+    lse = torch.empty((n_rows,), dtype=torch.float32, device=dev)
+    loss = torch.empty(tuple(target_shape) if red == _lib.REDUCTION_NONE else (), dtype=torch.float32, device=dev)
+    ws = _workspace(L.lce_forward_loss_workspace_bytes(n_rows, hidden_size, v, dtype, flags), dev)
+    with _on_device(dev):
+        _lib.check(
+            L.lce_forward_loss(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
+                               int(target1d.dtype == torch.int64), n_rows, hidden_size, v, dtype, ignore_index, red,
+                               lse.data_ptr(), loss.data_ptr(), None, ws.data_ptr(), ws.numel(), flags, _stream(dev)),
+            "lce_forward_loss",
+        )
+    return loss, lse
 
 
 def _forward(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, reduction: str,
@@ -210,6 +256,8 @@ def _forward(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, r
     rank, world = parallel.group_rank_size(process_group)
     hidden2d = hidden.view(n_rows, hidden_size)
     target1d = target.view(n_rows)
+    if world == 1 and vocab_start in (None, 0):
+        return _forward_single(hidden2d, weight, target1d, target.shape, red, ignore_index)
     stats = local_stats(hidden2d, weight, target1d, _resolve_vocab_start(vocab_start, rank, v_local),
                         _path_flags())
     loss, lse, _ = finalize(parallel.gather_stats(stats, process_group), target1d, reduction, ignore_index)
@@ -269,7 +317,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
         events = parallel.ready_events(dev, n_chunks)
         event_array = (ctypes.c_void_p * n_chunks)(*[e.cuda_event for e in events])
 
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _lib.check(
             L.lce_backward(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
                            int(target1d.dtype == torch.int64), logsumexp.data_ptr(), grad_out.data_ptr(), n_rows,
@@ -372,7 +420,7 @@ def debug_gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool, b_mn_major: b
     m, k = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
     n = b.shape[1] if b_mn_major else b.shape[0]
     out = torch.empty((m, n), dtype=torch.float32, device=a.device)
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         _lib.check(
             _lib.lib().lce_debug_gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, int(a_mn_major),
                                       int(b_mn_major), _DTYPE_CODE[a.dtype],

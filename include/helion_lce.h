@@ -122,6 +122,16 @@ int lce_finalize(const float* stats, int R, const void* target, int target_is_i6
                  int64_t ignore_index, int reduction, float* lse, float* loss, float* valid_count,
                  void* ws, size_t ws_bytes, void* stream);
 
+/* Forward in one call for an unsharded vocabulary: lce_forward_stats followed by lce_finalize, with the
+ * merge and the finalize fused (the statistics never reach memory). Replaces the whole of
+ * _linear_cross_entropy_forward (tritium/ops/cross_entropy.py:563-640). Outputs as lce_finalize.
+ * N must be > 0. */
+size_t lce_forward_loss_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags);
+int lce_forward_loss(const void* x, const void* w, const void* target, int target_is_i64, int64_t N,
+                     int64_t H, int64_t V, int dtype, int64_t ignore_index, int reduction, float* lse,
+                     float* loss, float* valid_count, void* ws, size_t ws_bytes, unsigned flags,
+                     void* stream);
+
 /* ---- backward --------------------------------------------------------------------------------
  * Replaces linear_cross_entropy_backward (tritium/ops/cross_entropy.py:863-959): the fused
  * small-shape kernel (:296-382) and the chunk loop of F.linear / in-place softmax-gradient /

@@ -174,9 +174,10 @@ def test_workspace_sizing_is_host_only_and_sane():
     # a tighter cap shrinks the G block; what it adds is fp32 partial-sum scratch of dX / dW size
     small = L.lce_backward_workspace_bytes(n, h, v, bf16, 0, 64 << 20)
     assert 0 < small <= (64 << 20) + 4 * (n * h + v * h) * 2
-    # one block covers everything when it fits: no partial-sum scratch at all
+    # one block covers everything when it fits; the only extra is the split-K slabs of the dX GEMM
+    # (a few 128 x 256 fp32 tiles) that let a problem with this few rows fill the GPU
     tiny = L.lce_backward_workspace_bytes(128, 64, 1024, bf16, 0, 0)
-    assert tiny < 128 * 1024 * 2 + 128 * 4 + 4096
+    assert tiny < 128 * 1024 * 2 + 16 * 2 * 128 * 256 * 4 + 8192
 
 
 def test_null_pointers_and_bad_enums_are_argument_errors():
