@@ -5,10 +5,13 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 ``helion_b200.build``) and an sm_100 device. There is no CPU or torch fallback.
 """
 
+from .ce_ops import cross_entropy, cross_entropy_backward
 from .install import install, uninstall
 from .ops import linear_cross_entropy, linear_cross_entropy_backward
 
 __all__ = [
+    "cross_entropy",
+    "cross_entropy_backward",
     "install",
     "linear_cross_entropy",
     "linear_cross_entropy_backward",

@@ -41,6 +41,11 @@ SIGNATURES = {
                              c_uint, c_size_t, c_void_p, c_void_p]),
     "lce_backward_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t, c_void_p, c_void_p,
                                   ctypes.POINTER(c_int64)]),
+    "lce_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "lce_ce_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lce_ce_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
+                                c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                c_uint, c_void_p]),
 }

@@ -10,6 +10,7 @@
 #include "../../include/helion_lce.h"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "ce_kernels.cuh"
 #include "row_kernels.cuh"
 
 namespace lce {
@@ -806,6 +807,157 @@ int lce_forward_stats_static(const void* x, const void* w, const void* target, i
             return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
         default:
             return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
+    }
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Cross-entropy on materialised logits
+// ---------------------------------------------------------------------------------------------
+namespace lce {
+namespace {
+
+struct CeLayout {
+    long long n_chunks, n_groups, row_stride;
+    size_t off_partial, off_loss_rows, off_rowscale, off_count, total;
+};
+
+long long ce_chunk(int dtype) { return dtype == LCE_DTYPE_F32 ? CeTile<float>::kChunk : CeTile<__half>::kChunk; }
+
+CeLayout ce_layout(long long N, long long V, int dtype) {
+    CeLayout l;
+    l.n_chunks = cdiv(V, ce_chunk(dtype));
+    l.n_groups = cdiv(l.n_chunks, kCeChunksPerCta);  // forward CTAs per row
+    l.row_stride = static_cast<long long>(align_up(static_cast<size_t>(N > 0 ? N : 1), 64));
+    size_t off = 0;
+    l.off_partial = off;
+    off += align_up(static_cast<size_t>(l.n_groups) * 3 * l.row_stride * sizeof(float), 256);
+    l.off_loss_rows = off;
+    off += align_up(static_cast<size_t>(l.row_stride) * sizeof(float), 256);
+    l.off_rowscale = off;
+    off += align_up(static_cast<size_t>(l.row_stride) * sizeof(float), 256);
+    l.off_count = off;
+    off += 256;
+    l.total = off;
+    return l;
+}
+
+template <class T>
+int ce_forward_impl(const void* logits, const void* tgt, int tgt_i64, long long N, long long V, long long ignore_index,
+                    const CeLayout& l, char* ws, float* lse, float* loss_rows, cudaStream_t s) {
+    const T* z = static_cast<const T*>(logits);
+    const bool vec = aligned16(logits) && (V * sizeof(T)) % 16 == 0;
+    float* partial = reinterpret_cast<float*>(ws + l.off_partial);
+    const int grid = static_cast<int>(N * l.n_groups);
+    const int nc = static_cast<int>(l.n_chunks), ng = static_cast<int>(l.n_groups);
+    if (l.n_groups == 1) {
+        if (vec) ce_row_stats_kernel<T, true, true><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
+        else ce_row_stats_kernel<T, false, true><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
+        LCE_COUNT_LAUNCH();
+        return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    }
+    if (vec) ce_row_stats_kernel<T, true, false><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
+    else ce_row_stats_kernel<T, false, false><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
+    LCE_COUNT_LAUNCH();
+    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    merge_partials_kernel<true><<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, s>>>(
+        partial, ng, l.row_stride, static_cast<int>(N), nullptr, tgt, tgt_i64, ignore_index, lse, loss_rows);
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+template <class T>
+int ce_backward_impl(const void* logits, const void* tgt, int tgt_i64, long long N, long long V, const float* lse,
+                     const float* rowscale, void* dlogits, cudaStream_t s) {
+    const bool vec = aligned16(logits) && aligned16(dlogits) && (V * sizeof(T)) % 16 == 0;
+    const long long n_chunks = cdiv(V, CeTile<T>::kChunk);
+    const int grid = static_cast<int>(N * n_chunks);
+    if (vec) ce_backward_kernel<T, true><<<grid, kCeThreads, 0, s>>>(static_cast<const T*>(logits), tgt, tgt_i64, V, (int)n_chunks, lse, rowscale, static_cast<T*>(dlogits));
+    else ce_backward_kernel<T, false><<<grid, kCeThreads, 0, s>>>(static_cast<const T*>(logits), tgt, tgt_i64, V, (int)n_chunks, lse, rowscale, static_cast<T*>(dlogits));
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+int check_ce_dims(long long N, long long V, int dtype, int reduction) {
+    if (N < 0 || V <= 0) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
+        return LCE_ERR_ARG;
+    if (N > 0x7fffff00ll || N * cdiv(V, ce_chunk(dtype)) > 0x7fffff00ll) return LCE_ERR_TOO_LARGE;
+    return LCE_OK;
+}
+
+}  // namespace
+}  // namespace lce
+
+extern "C" {
+
+size_t lce_ce_workspace_bytes(int64_t N, int64_t V, int dtype) {
+    if (N < 0 || V <= 0) return 0;
+    return ce_layout(N, V, dtype).total;
+}
+
+int lce_ce_forward(const void* logits, const void* target, int target_is_i64, int64_t N, int64_t V, int dtype,
+                   int64_t ignore_index, int reduction, float* lse, float* loss, float* valid_count, void* ws,
+                   size_t ws_bytes, void* stream) {
+    int rc = check_ce_dims(N, V, dtype, reduction);
+    if (rc) return rc;
+    if (N == 0) return LCE_ERR_ARG;  // the empty batch is the caller's business
+    if (!logits || !target || !lse || !loss || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    const CeLayout l = ce_layout(N, V, dtype);
+    if (ws_bytes < l.total) return LCE_ERR_WS_TOO_SMALL;
+    char* wsc = static_cast<char*>(ws);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* loss_rows = reduction == LCE_REDUCTION_NONE ? loss : reinterpret_cast<float*>(wsc + l.off_loss_rows);
+    switch (dtype) {
+        case LCE_DTYPE_BF16: rc = ce_forward_impl<__nv_bfloat16>(logits, target, target_is_i64, N, V, ignore_index, l, wsc, lse, loss_rows, s); break;
+        case LCE_DTYPE_F16: rc = ce_forward_impl<__half>(logits, target, target_is_i64, N, V, ignore_index, l, wsc, lse, loss_rows, s); break;
+        default: rc = ce_forward_impl<float>(logits, target, target_is_i64, N, V, ignore_index, l, wsc, lse, loss_rows, s);
+    }
+    if (rc) return rc;
+    if (reduction != LCE_REDUCTION_NONE || valid_count) {
+        reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
+                                              reduction == LCE_REDUCTION_MEAN ? 1 : 0,
+                                              reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    return LCE_OK;
+}
+
+int lce_ce_backward(const void* logits, const void* target, int target_is_i64, const float* lse,
+                    const float* grad_out, int64_t N, int64_t V, int dtype, int64_t ignore_index, int reduction,
+                    void* dlogits, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_ce_dims(N, V, dtype, reduction);
+    if (rc) return rc;
+    if (N == 0) return LCE_OK;
+    if (!logits || !target || !lse || !grad_out || !dlogits || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    const CeLayout l = ce_layout(N, V, dtype);
+    if (ws_bytes < l.total) return LCE_ERR_WS_TOO_SMALL;
+    char* wsc = static_cast<char*>(ws);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* rowscale = reinterpret_cast<float*>(wsc + l.off_rowscale);
+    float* count = reinterpret_cast<float*>(wsc + l.off_count);
+    const bool separate_count = reduction == LCE_REDUCTION_MEAN && N > 16384;
+    if (separate_count) {
+        count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
+        target, target_is_i64, static_cast<int>(N), ignore_index, grad_out, reduction == LCE_REDUCTION_NONE ? 1 : 0,
+        reduction == LCE_REDUCTION_MEAN ? 1 : 0, separate_count ? count : nullptr, rowscale);
+    LCE_COUNT_LAUNCH();
+    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    switch (dtype) {
+        case LCE_DTYPE_BF16: return ce_backward_impl<__nv_bfloat16>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
+        case LCE_DTYPE_F16: return ce_backward_impl<__half>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
+        default: return ce_backward_impl<float>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
     }
 }
 

@@ -13,9 +13,16 @@ import importlib
 import sys
 from types import ModuleType
 
-from . import ops
+from . import ce_ops, ops
 
-NAMES = ("linear_cross_entropy", "linear_cross_entropy_backward")
+# the fused op (the path this package exists for) and the plain op of the same reference file
+NAMES = ("linear_cross_entropy", "linear_cross_entropy_backward", "cross_entropy", "cross_entropy_backward")
+_IMPL = {
+    "linear_cross_entropy": ops.linear_cross_entropy,
+    "linear_cross_entropy_backward": ops.linear_cross_entropy_backward,
+    "cross_entropy": ce_ops.cross_entropy,
+    "cross_entropy_backward": ce_ops.cross_entropy_backward,
+}
 MODULES = ("tritium", "tritium.ops", "tritium.ops.cross_entropy")
 
 _saved: dict[tuple[str, str], object] = {}
@@ -39,7 +46,9 @@ def _targets(root: ModuleType | None) -> list[ModuleType]:
 
 
 def install(tritium_module: ModuleType | None = None) -> list[str]:
-    """Rebind the two names on ``tritium`` and its op modules; returns the rebound ``module.name`` list."""
+    """Rebind the four cross-entropy names on ``tritium`` and its op modules; returns the rebound
+    ``module.name`` list. (On ``tritium.ops`` the attribute ``cross_entropy`` is the function, which
+    shadows the submodule of the same name; it is the function that gets replaced.)"""
     rebound = []
     for mod in _targets(tritium_module):
         for name in NAMES:
@@ -48,7 +57,7 @@ def install(tritium_module: ModuleType | None = None) -> list[str]:
             key = (mod.__name__, name)
             if key not in _saved:
                 _saved[key] = getattr(mod, name)
-            setattr(mod, name, getattr(ops, name))
+            setattr(mod, name, _IMPL[name])
             rebound.append(f"{mod.__name__}.{name}")
     return rebound
 

@@ -161,6 +161,20 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
 int lce_backward_plan(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
                       size_t block_bytes, const void* x, const void* w, int64_t* out);
 
+/* ---- cross-entropy on materialised logits -------------------------------------------------------
+ * The plain op of the same reference file: tritium.cross_entropy (tritium/ops/cross_entropy.py:708-713,
+ * kernel :36-68) and tritium.cross_entropy_backward (:792-799, kernel :71-100). logits is [N, V]
+ * row-major in `dtype`. Outputs as lce_finalize: lse[N], loss (1 float, or N for NONE), optional
+ * valid_count. dlogits has the dtype of logits. One pass over the logits each way (bandwidth-bound);
+ * no limit on V (the reference refuses next_pow2(V) > 131072). N must be > 0 in the forward. */
+size_t lce_ce_workspace_bytes(int64_t N, int64_t V, int dtype);
+int lce_ce_forward(const void* logits, const void* target, int target_is_i64, int64_t N, int64_t V,
+                   int dtype, int64_t ignore_index, int reduction, float* lse, float* loss,
+                   float* valid_count, void* ws, size_t ws_bytes, void* stream);
+int lce_ce_backward(const void* logits, const void* target, int target_is_i64, const float* lse,
+                    const float* grad_out, int64_t N, int64_t V, int dtype, int64_t ignore_index,
+                    int reduction, void* dlogits, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- test hook -------------------------------------------------------------------------------
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
  * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b

@@ -190,6 +190,44 @@ def restated_backward(grad_out: torch.Tensor, hidden: torch.Tensor, weight: torc
 
 
 # ----------------------------------------------------------------------------------------------
+# the plain op on materialised logits (same reference file)
+# ----------------------------------------------------------------------------------------------
+def plain_expression(logits: torch.Tensor, target: torch.Tensor, *, reduction: str = "mean",
+                     ignore_index: int = -100, grad_out: torch.Tensor | None = None, want_grads: bool = True) -> dict:
+    """``F.cross_entropy(logits.float(), target)`` and its gradient: what the reference's tests compare
+    ``tritium.cross_entropy`` against (tests/tritium/test_cross_entropy.py:24-25, 40-42, 54-56)."""
+    z = logits.detach().float().clone().requires_grad_(want_grads)
+    loss = F.cross_entropy(z, target.long(), ignore_index=ignore_index, reduction=reduction)
+    out = {"loss": loss.detach(), "lse": torch.logsumexp(z.detach(), dim=-1)}
+    if want_grads:
+        loss.backward(torch.ones_like(loss) if grad_out is None else grad_out.detach().float().reshape(loss.shape))
+        out["dlogits"] = z.grad
+    return out
+
+
+def restated_plain_forward(logits: torch.Tensor, target: torch.Tensor) -> dict:
+    """The reference's row kernel (tritium/ops/cross_entropy.py:36-68): fp32 row max, sum of
+    exp(z - max), lse = log(sum) + max, nll = lse - z[target]; mean over ALL rows (:66-68)."""
+    z = logits.detach().float()
+    n = z.shape[0]
+    row_max = z.max(dim=1).values
+    lse = torch.log(torch.exp(z - row_max[:, None]).sum(dim=1)) + row_max
+    nll = lse - z.gather(1, target.long()[:, None])[:, 0]
+    return {"loss": nll.sum() if n == 1 else (nll / n).sum(), "lse": lse}
+
+
+def restated_plain_backward(grad_out: torch.Tensor, logits: torch.Tensor, target: torch.Tensor,
+                            lse: torch.Tensor) -> torch.Tensor:
+    """The reference's backward row kernel (:71-100): (exp(z - lse) - onehot) * grad_out / n_rows, computed
+    in fp32 and stored in the logits dtype."""
+    z = logits.detach().float()
+    n = z.shape[0]
+    g = torch.exp(z - lse[:, None])
+    g[torch.arange(n), target.long()] -= 1.0
+    return (g * (grad_out.detach().float().reshape(()) / n)).to(logits.dtype)
+
+
+# ----------------------------------------------------------------------------------------------
 # vocabulary sharding algebra (what each rank contributes and how the merge must come out)
 # ----------------------------------------------------------------------------------------------
 def shard_stats(hidden: torch.Tensor, weight_shard: torch.Tensor, target: torch.Tensor, vocab_start: int) -> torch.Tensor:

@@ -48,12 +48,26 @@ def case_list() -> list[dict]:
                   "grads": True, "grad_out": 0.37})
     cases.append({"name": "chunkloop-float32", "shape": (48,), "h": 72, "v": 300, "dtype": "float32",
                   "grads": True, "grad_out": 2.5})
+    # plain cross-entropy on materialised logits (reference tests :11-56): appended so that the
+    # seeds of the cases above never move
+    for dt in DTYPES:
+        for v in (16, 1024):
+            for n in (1, 128):
+                cases.append({"name": f"plain-fwd-{dt}-n{n}-v{v}", "op": "plain", "shape": (n,), "v": v, "dtype": dt,
+                              "grads": False})
+        cases.append({"name": f"plain-autograd-{dt}", "op": "plain", "shape": (64,), "v": 256, "dtype": dt,
+                      "grads": True, "grad_out": -0.8})
     return cases
 
 
 def make_case_inputs(case: dict, index: int) -> dict:
     g = torch.Generator(device="cpu").manual_seed(1000 + index)
     dt = DTYPES[case["dtype"]]
+    if case.get("op") == "plain":
+        logits = torch.randn(*case["shape"], case["v"], generator=g).to(dt)
+        target = torch.randint(0, case["v"], case["shape"], generator=g)
+        return {"logits": logits, "target": target,
+                "grad_out": torch.tensor(case.get("grad_out", 1.0), dtype=torch.float32)}
     hidden = torch.randn(*case["shape"], case["h"], generator=g).to(dt)
     weight = torch.randn(case["v"], case["h"], generator=g).to(dt)
     target = torch.randint(0, case["v"], case["shape"], generator=g)
@@ -63,7 +77,7 @@ def make_case_inputs(case: dict, index: int) -> dict:
 
 def input_checksums(inp: dict) -> dict:
     """float64 sums of the seeded inputs: lets a test notice if the CPU generator ever changes."""
-    return {k: float(inp[k].double().sum()) for k in ("hidden", "weight", "target")}
+    return {k: float(inp[k].double().sum()) for k in ("hidden", "weight", "logits", "target") if k in inp}
 
 
 def run_oracle() -> None:
@@ -72,8 +86,12 @@ def run_oracle() -> None:
     out = {}
     for i, case in enumerate(case_list()):
         inp = make_case_inputs(case, i)
-        ref = oracle.expression(inp["hidden"], inp["weight"], inp["target"], grad_out=inp["grad_out"],
-                                want_grads=case["grads"])
+        if case.get("op") == "plain":
+            ref = oracle.plain_expression(inp["logits"], inp["target"], grad_out=inp["grad_out"],
+                                          want_grads=case["grads"])
+        else:
+            ref = oracle.expression(inp["hidden"], inp["weight"], inp["target"], grad_out=inp["grad_out"],
+                                    want_grads=case["grads"])
         out[case["name"]] = {"case": case, "input_checksums": input_checksums(inp), "expected": ref}
     torch.save(out, HERE / "oracle_cases.pt")
     print(f"wrote {HERE / 'oracle_cases.pt'} ({len(out)} cases)")
@@ -94,6 +112,20 @@ def run_reference(dest: str) -> None:
                      "triton": __import__("triton").__version__}}
     for i, case in enumerate(case_list()):
         inp = make_case_inputs(case, i)
+        if case.get("op") == "plain":
+            z = inp["logits"].to(dev)
+            t = inp["target"].to(dev)
+            loss, lse = ref_ce._cross_entropy_forward(z, t)
+            rec = {"loss": loss.cpu(), "lse": lse.cpu()}
+            if case["grads"]:
+                zg = z.clone().requires_grad_(True)
+                tritium.cross_entropy(zg, t).backward(inp["grad_out"].to(dev))
+                rec["dlogits"] = zg.grad.cpu()
+                rec["dlogits_direct"] = tritium.cross_entropy_backward(inp["grad_out"].to(dev), z, t, lse).cpu()
+            torch.cuda.synchronize()
+            out[case["name"]] = rec
+            print(case["name"], float(rec["loss"]))
+            continue
         h = inp["hidden"].to(dev)
         w = inp["weight"].to(dev)
         t = inp["target"].to(dev)

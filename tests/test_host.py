@@ -82,6 +82,30 @@ def test_backward_validation_messages(any_device):
             ops.check_backward_inputs(*args)
 
 
+def test_plain_cross_entropy_validation_messages(any_device, monkeypatch):
+    from helion_b200 import ce_ops
+
+    monkeypatch.setattr(ce_ops, "_need_cuda", lambda name, t: None)
+    z, t = torch.randn(4, 16), torch.randint(16, (4,))
+    for args, msg in [
+        ((z.double(), t), "logits must have one of these dtypes"),
+        ((z[0], t), r"logits must be a 2D tensor shaped \(n_rows, vocab_size\)."),
+        ((z, t[None]), "target must be a 1D tensor."),
+        ((z, torch.randint(16, (5,))), r"Shape mismatch: target has shape \(5,\), expected \(4,\)."),
+        ((torch.randn(16, 4).t(), t), "logits must be contiguous for tritium.cross_entropy."),
+    ]:
+        with pytest.raises(ValueError, match=msg):
+            ce_ops.check_inputs(*args)
+    assert ce_ops.check_inputs(torch.randn(3, 200000), torch.randint(9, (3,))) == (3, 200000)  # no vocabulary cap
+
+
+def test_plain_cross_entropy_rejects_cpu_tensors():
+    import helion_b200
+
+    with pytest.raises(ValueError, match="CUDA tensor"):  # the reference's own test (test_cross_entropy.py:112-114)
+        helion_b200.cross_entropy(torch.randn(4, 16), torch.randint(16, (4,)))
+
+
 def test_unknown_reduction_is_rejected(any_device):
     with pytest.raises(ValueError, match="reduction must be one of"):
         ops._check_reduction("batchmean")
@@ -95,28 +119,35 @@ def _fake_tritium():
     for mod in (root, sub, leaf):
         mod.linear_cross_entropy = lambda *a: "reference forward"
         mod.linear_cross_entropy_backward = lambda *a: "reference backward"
-        mod.cross_entropy = lambda *a: "plain ce"
+        mod.cross_entropy = lambda *a: "reference plain forward"
+        mod.cross_entropy_backward = lambda *a: "reference plain backward"
+        mod.matmul = lambda *a: "another op"
     root.ops = sub
-    sub.cross_entropy = leaf.cross_entropy  # the attribute is the function, as in the reference
+    # on tritium.ops the attribute `cross_entropy` is the function (it shadows the submodule)
     for mod in (root, sub, leaf):
         sys.modules[mod.__name__] = mod
     return root, sub, leaf
 
 
 def test_install_rebinds_all_three_modules_and_uninstall_restores():
+    from helion_b200 import ce_ops
+
     root, sub, leaf = _fake_tritium()
     try:
         rebound = install(root)
-        assert len(rebound) == 6
+        assert len(rebound) == 12
         for mod in (root, sub, leaf):
             assert mod.linear_cross_entropy is ops.linear_cross_entropy
             assert mod.linear_cross_entropy_backward is ops.linear_cross_entropy_backward
-            assert mod.cross_entropy() == "plain ce"  # everything else is left alone
+            assert mod.cross_entropy is ce_ops.cross_entropy
+            assert mod.cross_entropy_backward is ce_ops.cross_entropy_backward
+            assert mod.matmul() == "another op"  # everything else is left alone
         install(root)  # idempotent: the saved originals are not overwritten by our own functions
         uninstall(root)
         for mod in (root, sub, leaf):
             assert mod.linear_cross_entropy() == "reference forward"
             assert mod.linear_cross_entropy_backward() == "reference backward"
+            assert mod.cross_entropy() == "reference plain forward"
     finally:
         for name in list(sys.modules):
             if name.startswith("fake_tritium"):
