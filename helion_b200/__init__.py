@@ -7,6 +7,7 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 
 from .ce_ops import cross_entropy, cross_entropy_backward
 from .install import install, uninstall
+from .matmul_ops import matmul, matmul_vec
 from .ops import linear_cross_entropy, linear_cross_entropy_backward
 
 __all__ = [
@@ -15,5 +16,7 @@ __all__ = [
     "install",
     "linear_cross_entropy",
     "linear_cross_entropy_backward",
+    "matmul",
+    "matmul_vec",
     "uninstall",
 ]

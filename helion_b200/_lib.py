@@ -38,7 +38,8 @@ SIGNATURES = {
     "lce_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t]),
     "lce_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
-                             c_uint, c_size_t, c_void_p, c_void_p]),
+                             c_uint, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "lce_dx_reduce_gather": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "lce_backward_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t, c_void_p, c_void_p,
                                   ctypes.POINTER(c_int64)]),
     "lce_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
@@ -46,9 +47,18 @@ SIGNATURES = {
                                c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "lce_ce_backward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64,
                                 c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lce_matmul_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
+    "lce_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int, c_int64,
+                           c_int64, c_int, c_void_p, c_size_t, c_uint, c_void_p]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                c_uint, c_void_p]),
 }
+
+
+class PeerScatter(ctypes.Structure):
+    """``lce_peer_scatter`` of include/helion_lce.h."""
+
+    _fields_ = [("staging", c_void_p * 8), ("rank", c_int), ("world", c_int)]
 
 
 class LceError(RuntimeError):

@@ -206,6 +206,8 @@ struct EpiGrad {
 // library, so it is laid out for coalescing, not as a matrix: float4 index
 //   ((tile * bn/4 + col/4) * 128 + row_in_tile).
 // ---------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+
 enum StoreMode { kStoreDirect = 0, kStoreFirst = 1, kStoreAccum = 2, kStoreLast = 3, kStoreSlice = 4 };
 
 template <class T>
@@ -217,12 +219,30 @@ struct EpiStore {
         float* scratch;
         int mode;
         long long slab_floats;  // kStoreSlice: distance between the slabs of consecutive k slices
+        // Peer scatter (peer_world > 0, T = float only): the finished row does not go to `out` but
+        // to the GPU that owns it in a reduce-scatter over row slices. Row g (= row_off + local row)
+        // belongs to rank g / rows_per_rank, and lands in that rank's staging buffer
+        // [world][rows_per_rank][ldo] in the slot of the sending rank. The stores go over NVLink from
+        // inside the GEMM epilogue; nothing waits on another GPU here.
+        T* peer[kMaxPeers];
+        int peer_world, peer_rank;
+        int rows_per_rank;
+        int row_off;
     };
     struct State {
         int row;
+        T* dst;  // start of this thread's output row
     };
-    static __device__ __forceinline__ void begin(State& st, const Params&, const TileCtx& tc) {
+    static __device__ __forceinline__ void begin(State& st, const Params& p, const TileCtx& tc) {
         st.row = tc.m_tile * kBM + tc.row_in_tile;
+        if (p.peer_world > 0) {
+            const int g = p.row_off + st.row;
+            const int owner = g / p.rows_per_rank;
+            st.dst = p.peer[owner < p.peer_world ? owner : 0] +
+                     (static_cast<long long>(p.peer_rank) * p.rows_per_rank + (g - owner * p.rows_per_rank)) * p.ldo;
+        } else {
+            st.dst = p.out + static_cast<long long>(st.row) * p.ldo;
+        }
     }
     static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
                                                  int col0, float (&v)[32]) {
@@ -250,7 +270,7 @@ struct EpiStore {
             }
         }
         if (st.row >= p.rows || gcol0 >= p.cols) return;
-        store_row32<T>(p.out + static_cast<long long>(st.row) * p.ldo + gcol0, v, p.cols - gcol0);
+        store_row32<T>(st.dst + gcol0, v, p.cols - gcol0);
     }
     static __device__ __forceinline__ void end(State&, const Params&, const TileCtx&) {}
 };

@@ -377,7 +377,7 @@ template <class T, class TDx>
 int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void* x, const void* w,
                   const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
                   long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, void* const* dx_events,
-                  cudaStream_t stream) {
+                  const lce_peer_scatter* scatter, cudaStream_t stream) {
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
     const T* xp = static_cast<const T*>(x);
     const T* wp = static_cast<const T*>(w);
@@ -426,9 +426,20 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 ep.scratch = reinterpret_cast<float*>(ws + p.off_dx_scratch);
                 ep.mode = store_mode(cb, p.n_cblk);
                 ep.slab_floats = p.dx_slab_floats;
+                ep.peer_world = 0;
+                if constexpr (std::is_same<TDx, float>::value) {
+                    if (scatter != nullptr) {  // finished rows go straight to the GPUs that own them
+                        ep.peer_world = scatter->world;
+                        ep.peer_rank = scatter->rank;
+                        ep.rows_per_rank = static_cast<int>(cdiv(N, scatter->world));
+                        ep.row_off = static_cast<int>(r0);
+                        for (int k = 0; k < scatter->world; ++k) ep.peer[k] = static_cast<float*>(scatter->staging[k]);
+                        ep.out = nullptr;
+                    }
+                }
                 const Mat b{wp + c0 * H, nc, H, H};
                 // few output tiles (short row chunk): cut the vocabulary contraction into slices
-                const int splits = (p.dx_splits > 1 && nr == p.nr) ? p.dx_splits : 1;
+                const int splits = (p.dx_splits > 1 && nr == p.nr && scatter == nullptr) ? p.dx_splits : 1;
                 if (splits > 1) ep.mode = kStoreSlice;
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
@@ -464,6 +475,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
                 ep.mode = store_mode(rb, p.n_rblk);
                 ep.slab_floats = 0;
+                ep.peer_world = 0;
                 const Mat b{xp + r0 * H, nr, H, H};
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
@@ -662,13 +674,21 @@ int lce_backward_plan(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags
 int lce_backward(const void* x, const void* w, const void* target, int target_is_i64, const float* lse,
                  const float* grad_out, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
                  int64_t ignore_index, int reduction, void* dx, void* dw, void* ws, size_t ws_bytes,
-                 unsigned flags, size_t block_bytes, void* const* dx_events, void* stream) {
+                 unsigned flags, size_t block_bytes, void* const* dx_events, const lce_peer_scatter* scatter,
+                 void* stream) {
     int rc = check_dims(N, H, V, dtype);
     if (rc) return rc;
     if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
         return LCE_ERR_ARG;
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
-    if ((need_dx && !dx && N > 0) || (need_dw && !dw)) return LCE_ERR_ARG;
+    if (scatter != nullptr) {
+        if (!(flags & LCE_FLAG_DX_F32) || scatter->world < 1 || scatter->world > kMaxPeers || scatter->rank < 0 ||
+            scatter->rank >= scatter->world || (H % 4) != 0)
+            return LCE_ERR_ARG;
+        for (int k = 0; k < scatter->world; ++k)
+            if (!scatter->staging[k] || !aligned16(scatter->staging[k])) return LCE_ERR_ARG;
+    }
+    if ((need_dx && !dx && !scatter && N > 0) || (need_dw && !dw)) return LCE_ERR_ARG;
     DeviceInfo* d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -703,9 +723,9 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
 #define LCE_BWD(T)                                                                                          \
     (dx32 ? backward_impl<T, float>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
-                                    dx, dw, wsc, flags, dx_events, s)                                       \
+                                    dx, dw, wsc, flags, dx_events, scatter, s)                              \
           : backward_impl<T, T>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
-                                dw, wsc, flags, dx_events, s))
+                                dw, wsc, flags, dx_events, nullptr, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
         case LCE_DTYPE_F16: return LCE_BWD(__half);
@@ -731,6 +751,7 @@ int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t 
     ep.scratch = nullptr;
     ep.mode = kStoreDirect;
     ep.slab_floats = 0;
+    ep.peer_world = 0;
     const Mat am = a_mn ? Mat{a, K, M, M} : Mat{a, M, K, K};
     const Mat bm = b_mn ? Mat{b, K, N, N} : Mat{b, N, K, K};
 #define LCE_DBG(AMN, BMN)                                                                               \
@@ -811,6 +832,37 @@ int lce_forward_stats_static(const void* x, const void* w, const void* target, i
 }
 
 }  // extern "C"
+
+extern "C" int lce_dx_reduce_gather(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
+                                    void* const* out_ptrs, void* stream) {
+    if (!staging || !out_ptrs || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || N <= 0 || H <= 0 ||
+        (H % 4) != 0)
+        return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const long long rpr = cdiv(N, world);
+    const long long row0 = rpr * rank;
+    const long long n_rows = row0 >= N ? 0 : (N - row0 < rpr ? N - row0 : rpr);
+    if (n_rows == 0) return LCE_OK;
+    PeerOutputs outs;
+    for (int k = 0; k < world; ++k) {
+        if (!out_ptrs[k]) return LCE_ERR_ARG;
+        outs.out[k] = out_ptrs[k];
+    }
+    const long long quads = n_rows * (H / 4);
+    const int blocks = static_cast<int>(cdiv(quads, 256) < 148 * 16 ? cdiv(quads, 256) : 148 * 16);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float* st = static_cast<const float*>(staging);
+    switch (dtype) {
+        case LCE_DTYPE_BF16: dx_reduce_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
+        case LCE_DTYPE_F16: dx_reduce_gather_kernel<__half><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
+        case LCE_DTYPE_F32: dx_reduce_gather_kernel<float><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
+        default: return LCE_ERR_ARG;
+    }
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Cross-entropy on materialised logits
@@ -958,6 +1010,110 @@ int lce_ce_backward(const void* logits, const void* target, int target_is_i64, c
         case LCE_DTYPE_BF16: return ce_backward_impl<__nv_bfloat16>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
         case LCE_DTYPE_F16: return ce_backward_impl<__half>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
         default: return ce_backward_impl<float>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
+    }
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Plain matrix product on the same GEMM cores
+// ---------------------------------------------------------------------------------------------
+namespace lce {
+namespace {
+
+struct MatmulPlan {
+    bool use_tc;
+    int splits;
+    long long slab_floats;
+    size_t ws_bytes;
+};
+
+MatmulPlan plan_matmul(long long M, long long N, long long K, int dtype, bool aligned, unsigned flags) {
+    MatmulPlan p;
+    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
+    p.use_tc = dtype != LCE_DTYPE_F32 && aligned && !(flags & LCE_FLAG_FORCE_SIMT);
+    p.splits = p.use_tc ? choose_k_splits(M, N, K) : 1;
+    p.slab_floats = cdiv(M, 2 * kBM) * 2 * cdiv(N, kBN) * kBM * kBN;
+    p.ws_bytes = p.splits > 1 ? static_cast<size_t>(p.splits) * p.slab_floats * sizeof(float) : 0;
+    return p;
+}
+
+template <class T>
+int matmul_impl(const DeviceInfo& d, const MatmulPlan& p, const Mat& a, bool a_mn, const Mat& b, bool b_mn, void* c,
+                long long M, long long N, long long K, long long ldc, void* ws, cudaStream_t s) {
+    typename EpiStore<T>::Params ep;
+    ep.out = static_cast<T*>(c);
+    ep.ldo = ldc;
+    ep.rows = static_cast<int>(M);
+    ep.cols = static_cast<int>(N);
+    ep.scratch = static_cast<float*>(ws);
+    ep.mode = p.splits > 1 ? kStoreSlice : kStoreDirect;
+    ep.slab_floats = p.slab_floats;
+    ep.peer_world = 0;
+    if (!p.use_tc) return launch_simt<T, EpiStore<T>>(d, a, a_mn, b, b_mn, M, N, K, ep, s);
+    int rc = LCE_ERR_ARG;
+    if constexpr (sizeof(T) == 2) {
+        constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+        // tiles that run together share a B panel when there are many row tiles, an A panel otherwise
+        const int m_fastest = cdiv(M, kBM) >= cdiv(N, kBN) ? 1 : 0;
+        if (!a_mn && !b_mn) rc = launch_tc<false, false, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else if (!a_mn && b_mn) rc = launch_tc<false, true, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else if (a_mn && !b_mn) rc = launch_tc<true, false, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        if (rc == LCE_OK && p.splits > 1) {
+            const int m_tiles = static_cast<int>(cdiv(M, kBM)), n_tiles = static_cast<int>(cdiv(N, kBN));
+            const long long quads = static_cast<long long>(m_tiles) * n_tiles * (kBN / 4) * kBM;
+            const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
+            splitk_reduce_kernel<T><<<blocks, 256, 0, s>>>(ep.scratch, p.splits, p.slab_floats, m_tiles, n_tiles, kBN,
+                                                          static_cast<int>(M), static_cast<int>(N), ep.out, ldc);
+            LCE_COUNT_LAUNCH();
+            if (cudaGetLastError() != cudaSuccess) rc = LCE_ERR_CUDA;
+        }
+    }
+    return rc;
+}
+
+bool matmul_aligned(const void* a, const void* b, long long lda, long long ldb) {
+    return aligned16(a) && aligned16(b) && lda % 8 == 0 && ldb % 8 == 0;
+}
+
+}  // namespace
+}  // namespace lce
+
+extern "C" {
+
+size_t lce_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype, unsigned flags) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return plan_matmul(M, N, K, dtype, true, flags).ws_bytes;
+}
+
+int lce_matmul(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int a_mn_major, int64_t lda,
+               int b_mn_major, int64_t ldb, int64_t ldc, int dtype, void* ws, size_t ws_bytes, unsigned flags,
+               void* stream) {
+    if (M < 0 || N < 0 || K < 0 || lda <= 0 || ldb <= 0 || ldc <= 0) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if (M > 0x7fffff00ll || N > 0x7fffff00ll || K > 0x7fffff00ll) return LCE_ERR_TOO_LARGE;
+    if (M == 0 || N == 0) return LCE_OK;
+    if (!c) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) {  // an empty contraction is all zeros
+        if (ldc != N) return LCE_ERR_ARG;
+        return cudaMemsetAsync(c, 0, static_cast<size_t>(M) * N * elem_size(dtype), s) == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    }
+    if (!a || !b) return LCE_ERR_ARG;
+    const bool aligned = matmul_aligned(a, b, lda, ldb);
+    if ((flags & LCE_FLAG_FORCE_TC) && (dtype == LCE_DTYPE_F32 || !aligned)) return dtype == LCE_DTYPE_F32 ? LCE_ERR_ARG : LCE_ERR_ALIGN;
+    const MatmulPlan p = plan_matmul(M, N, K, dtype, aligned, flags);
+    if (p.ws_bytes > 0 && (!ws || ws_bytes < p.ws_bytes)) return LCE_ERR_WS_TOO_SMALL;
+    const Mat am = a_mn_major ? Mat{a, K, M, lda} : Mat{a, M, K, lda};
+    const Mat bm = b_mn_major ? Mat{b, K, N, ldb} : Mat{b, N, K, ldb};
+    switch (dtype) {
+        case LCE_DTYPE_BF16: return matmul_impl<__nv_bfloat16>(*d, p, am, a_mn_major, bm, b_mn_major, c, M, N, K, ldc, ws, s);
+        case LCE_DTYPE_F16: return matmul_impl<__half>(*d, p, am, a_mn_major, bm, b_mn_major, c, M, N, K, ldc, ws, s);
+        default: return matmul_impl<float>(*d, p, am, a_mn_major, bm, b_mn_major, c, M, N, K, ldc, ws, s);
     }
 }
 

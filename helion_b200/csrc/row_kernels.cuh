@@ -201,4 +201,42 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ scratch, int slic
     }
 }
 
+// Second half of the dX reduce-scatter + all-gather across vocabulary shards. `staging` is THIS GPU's
+// buffer [world][rows_per_rank][H] fp32, filled by every rank's dX epilogue (slot = sending rank) with the
+// partial sums of the rows this GPU owns. Each thread adds the `world` partials of four columns in rank
+// order (the same order on every run), rounds once to T and stores the result into the final dX buffer of
+// EVERY rank (peer stores), rows [row0, row0 + n_rows).
+struct PeerOutputs {
+    void* out[kMaxPeers];
+};
+
+template <class T>
+__global__ void dx_reduce_gather_kernel(const float* __restrict__ staging, int world, long long rows_per_rank,
+                                        long long H, long long row0, long long n_rows, PeerOutputs outs) {
+    const long long quads_per_row = H / 4;
+    const long long total = n_rows * quads_per_row;
+    const long long slot_floats = rows_per_rank * H;
+    for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
+         q += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = q / quads_per_row;
+        const long long c = (q % quads_per_row) * 4;
+        const float* src = staging + r * H + c;
+        float4 acc = *reinterpret_cast<const float4*>(src);
+        for (int k = 1; k < world; ++k) {
+            const float4 v = *reinterpret_cast<const float4*>(src + k * slot_floats);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        alignas(8) T packed[4] = {Cvt<T>::from_f(acc.x), Cvt<T>::from_f(acc.y), Cvt<T>::from_f(acc.z),
+                                  Cvt<T>::from_f(acc.w)};
+        for (int k = 0; k < world; ++k) {
+            T* dst = static_cast<T*>(outs.out[k]) + (row0 + r) * H + c;
+            if constexpr (sizeof(T) == 2) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(packed);
+            else *reinterpret_cast<float4*>(dst) = acc;
+        }
+    }
+}
+
 }  // namespace lce

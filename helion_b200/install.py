@@ -13,17 +13,21 @@ import importlib
 import sys
 from types import ModuleType
 
-from . import ce_ops, ops
+from . import ce_ops, matmul_ops, ops
 
-# the fused op (the path this package exists for) and the plain op of the same reference file
-NAMES = ("linear_cross_entropy", "linear_cross_entropy_backward", "cross_entropy", "cross_entropy_backward")
+# the fused op (the path this package exists for), the plain op of the same reference file, and the
+# matrix product that runs on the same GEMM cores
+NAMES = ("linear_cross_entropy", "linear_cross_entropy_backward", "cross_entropy", "cross_entropy_backward",
+         "matmul", "matmul_vec")
 _IMPL = {
+    "matmul": matmul_ops.matmul,
+    "matmul_vec": matmul_ops.matmul_vec,
     "linear_cross_entropy": ops.linear_cross_entropy,
     "linear_cross_entropy_backward": ops.linear_cross_entropy_backward,
     "cross_entropy": ce_ops.cross_entropy,
     "cross_entropy_backward": ce_ops.cross_entropy_backward,
 }
-MODULES = ("tritium", "tritium.ops", "tritium.ops.cross_entropy")
+MODULES = ("tritium", "tritium.ops", "tritium.ops.cross_entropy", "tritium.ops.matmul")
 
 _saved: dict[tuple[str, str], object] = {}
 
@@ -33,7 +37,7 @@ def _targets(root: ModuleType | None) -> list[ModuleType]:
     # (tritium/ops/__init__.py), so the submodules are taken from the import system, not via getattr.
     base = MODULES[0] if root is None else root.__name__
     mods = [importlib.import_module(base) if root is None else root]
-    for suffix in (".ops", ".ops.cross_entropy"):
+    for suffix in (".ops", ".ops.cross_entropy", ".ops.matmul"):
         name = base + suffix
         mod = sys.modules.get(name)
         if mod is None:
@@ -46,7 +50,7 @@ def _targets(root: ModuleType | None) -> list[ModuleType]:
 
 
 def install(tritium_module: ModuleType | None = None) -> list[str]:
-    """Rebind the four cross-entropy names on ``tritium`` and its op modules; returns the rebound
+    """Rebind the cross-entropy and matmul names on ``tritium`` and its op modules; returns the rebound
     ``module.name`` list. (On ``tritium.ops`` the attribute ``cross_entropy`` is the function, which
     shadows the submodule of the same name; it is the function that gets replaced.)"""
     rebound = []

@@ -306,9 +306,12 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     vstart = _resolve_vocab_start(vocab_start, rank, v_local)
     ws = _workspace(L.lce_backward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags, block), dev)
 
-    # Sharded: the partial dX of each row chunk is summed over the group on a side stream as soon as
-    # the library signals that chunk final, while the remaining dW GEMMs run on the main stream.
-    events, event_array, chunk_rows = None, None, n_rows
+    # Sharded: two ways to sum the partial dX over the group.
+    #  "p2p" (default): the dX GEMM's epilogue stores finished rows straight into the owning rank's staging
+    #        buffer over NVLink (reduce-scatter inside the GEMM); a small kernel then sums and all-gathers.
+    #  "nccl": fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library signals
+    #        the chunk final, while the remaining dW GEMMs run on the main stream.
+    events, event_array, chunk_rows, scatter, peers = None, None, n_rows, None, None
     if sharded and dx is not None:
         plan = (ctypes.c_int64 * 4)()
         _lib.check(L.lce_backward_plan(n_rows, hidden_size, v_local, dtype, flags, block, hidden2d.data_ptr(),
@@ -316,18 +319,51 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
         chunk_rows, n_chunks = int(plan[0]), int(plan[2])
         events = parallel.ready_events(dev, n_chunks)
         event_array = (ctypes.c_void_p * n_chunks)(*[e.cuda_event for e in events])
+        if _dx_reduce_mode() == "p2p" and hidden_size % 4 == 0 and world <= 8:
+            peers = parallel.peer_buffers(process_group, n_rows, hidden_size, hidden2d.dtype, dev)
+            scatter = _lib.PeerScatter()
+            for k, ptr in enumerate(peers.staging_ptrs):
+                scatter.staging[k] = ptr
+            scatter.rank, scatter.world = rank, world
+            dx = None  # nothing is written locally: rows leave through the epilogue
 
     with _on_device(dev):
         _lib.check(
             L.lce_backward(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
                            int(target1d.dtype == torch.int64), logsumexp.data_ptr(), grad_out.data_ptr(), n_rows,
                            hidden_size, v_local, vstart, dtype, ignore_index, red, _ptr(dx), _ptr(dw), ws.data_ptr(),
-                           ws.numel(), flags, block, event_array, _stream(dev)),
+                           ws.numel(), flags, block, event_array, ctypes.byref(scatter) if scatter is not None else None,
+                           _stream(dev)),
             "lce_backward",
         )
-    if sharded and dx is not None:
+    if peers is not None:
+        dx = _finish_peer_reduce(peers, events, n_rows, hidden_size, dtype, dev)
+    elif sharded and dx is not None:
         dx = parallel.reduce_dx_chunks(dx, chunk_rows, events, hidden2d.dtype, process_group)
     return dx, dw
+
+
+def _dx_reduce_mode() -> str:
+    return os.environ.get("HELION_B200_DX_REDUCE", "p2p")
+
+
+def _finish_peer_reduce(peers, events, n_rows: int, hidden_size: int, dtype: int, dev: torch.device) -> torch.Tensor:
+    """Second half of the fused dX reduction, on the side stream so that it overlaps the remaining dW GEMMs:
+    once this rank's last dX rows have left (event), order the ranks, sum + all-gather, order again."""
+    L = _lib.lib()
+    main = torch.cuda.current_stream(dev)
+    side = parallel.comm_stream(dev)
+    side.wait_event(events[-1])
+    with torch.cuda.stream(side):
+        peers.order_ranks()  # every rank's partial rows have landed in their owners' staging buffers
+        out_ptrs = (ctypes.c_void_p * peers.world)(*peers.final_ptrs)
+        _lib.check(L.lce_dx_reduce_gather(peers.staging.data_ptr(), peers.world, peers.rank, n_rows, hidden_size, dtype,
+                                          out_ptrs, side.cuda_stream), "lce_dx_reduce_gather")
+        peers.order_ranks()  # every rank's slice has been stored everywhere; staging may be reused
+        dx = peers.final.clone()
+    main.wait_stream(side)
+    dx.record_stream(main)
+    return dx
 
 
 def linear_cross_entropy_backward(

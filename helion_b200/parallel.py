@@ -107,3 +107,47 @@ def reduce_dx_chunks(dx_partial: torch.Tensor, chunk_rows: int, events, out_dtyp
                             group=process_group)
     main.wait_stream(side)
     return dx_partial if dx_partial.dtype == out_dtype else dx_partial.to(out_dtype)
+
+
+# ---- dX reduce-scatter fused into the GEMM epilogue (peer stores over NVLink) ----------------------
+class PeerBuffers:
+    """Symmetric (peer-mapped) buffers of one (group, N, H, dtype) problem, allocated once and reused:
+
+    * ``staging``  [world, rows_per_rank, H] fp32 on every rank: rank r's dX epilogue stores the partial
+      rows owned by rank o into slot r of rank o's staging buffer;
+    * ``final``    [N, H] in the op dtype on every rank: the owner of a row slice sums its ``world`` slots
+      and stores the rounded result into every rank's ``final``.
+
+    Two tiny all-reduces order the ranks (everyone has scattered before anyone sums; everyone has
+    gathered before the buffers are reused). No kernel of this package waits on another GPU.
+    """
+
+    def __init__(self, process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.rank, self.world = group_rank_size(process_group)
+        self.group = process_group
+        self.rows_per_rank = -(-n_rows // self.world)
+        self.staging = symm_mem.empty((self.world, self.rows_per_rank, hidden), dtype=torch.float32, device=device)
+        self.final = symm_mem.empty((n_rows, hidden), dtype=dtype, device=device)
+        self._staging_handle = symm_mem.rendezvous(self.staging, process_group)
+        self._final_handle = symm_mem.rendezvous(self.final, process_group)
+        self.staging_ptrs = [int(p) for p in self._staging_handle.buffer_ptrs]
+        self.final_ptrs = [int(p) for p in self._final_handle.buffer_ptrs]
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def order_ranks(self) -> None:
+        """Stream-ordered barrier: a 4-byte all-reduce on the current stream."""
+        import torch.distributed as dist
+
+        dist.all_reduce(self.flag, group=self.group)
+
+
+_peer_buffers: dict[tuple, PeerBuffers] = {}
+
+
+def peer_buffers(process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype, device: torch.device) -> PeerBuffers:
+    key = (id(process_group), n_rows, hidden, dtype, device.index)
+    if key not in _peer_buffers:
+        _peer_buffers[key] = PeerBuffers(process_group, n_rows, hidden, dtype, device)
+    return _peer_buffers[key]

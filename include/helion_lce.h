@@ -146,13 +146,32 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
  * dx_events: NULL, or one cudaEvent_t per row chunk of lce_backward_plan(); event i is recorded on
  * `stream` as soon as the dx rows of chunk i are final (before the remaining dW work), so that a
  * caller can start reducing partial dx across ranks on another stream while this call's GEMMs run. */
+/* Optional fusion of the cross-rank dX reduction into the dX GEMM (vocabulary-parallel runs; new, the
+ * reference is single-GPU). With a non-NULL `scatter` (and LCE_FLAG_DX_F32) lce_backward does not write
+ * `dx`: the epilogue of the dX GEMM stores every finished fp32 row directly into the staging buffer of
+ * the rank that owns the row in a reduce-scatter over row slices (rows_per_rank = ceil(N / world),
+ * owner = row / rows_per_rank), through peer pointers over NVLink. staging[k] is rank k's buffer of
+ * world * rows_per_rank * H floats, 16-byte aligned (peer-mapped device memory, e.g. symmetric memory);
+ * this rank writes slot `rank` of each. Plain stores only: no TMA and no multicast touch peer memory, and
+ * no kernel waits on another GPU - the caller orders the ranks (a barrier) before lce_dx_reduce_gather
+ * sums the world slots of this rank's rows in rank order, rounds once and stores the result into every
+ * rank's final dX buffer (out_ptrs[k], [N, H] in `dtype`). */
+typedef struct {
+    void* staging[8];
+    int rank;
+    int world;
+} lce_peer_scatter;
+
+int lce_dx_reduce_gather(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
+                         void* const* out_ptrs, void* stream);
+
 size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
                                     size_t block_bytes);
 int lce_backward(const void* x, const void* w, const void* target, int target_is_i64,
                  const float* lse, const float* grad_out, int64_t N, int64_t H, int64_t V_local,
                  int64_t vocab_start, int dtype, int64_t ignore_index, int reduction, void* dx,
                  void* dw, void* ws, size_t ws_bytes, unsigned flags, size_t block_bytes,
-                 void* const* dx_events, void* stream);
+                 void* const* dx_events, const lce_peer_scatter* scatter, void* stream);
 
 /* The block grid lce_backward will use for these arguments (x and w only decide, by their
  * alignment, which kernel family runs): out[0] = rows per row chunk, out[1] = vocabulary columns per
@@ -174,6 +193,20 @@ int lce_ce_forward(const void* logits, const void* target, int target_is_i64, in
 int lce_ce_backward(const void* logits, const void* target, int target_is_i64, const float* lse,
                     const float* grad_out, int64_t N, int64_t V, int dtype, int64_t ignore_index,
                     int reduction, void* dlogits, void* ws, size_t ws_bytes, void* stream);
+
+/* ---- plain matrix product --------------------------------------------------------------------------
+ * c[M, N] = A[M, K] * B[K, N] in `dtype` with fp32 accumulation, on the GEMM cores of the fused op
+ * (tcgen05 for 16-bit inputs with 16-byte aligned bases and pitches, CUDA cores otherwise; a short M with
+ * a long K is split along K and summed in a fixed order). Replaces the launches of tritium.matmul /
+ * matmul_vec (tritium/ops/matmul.py:47-129, 252-309): forward, and both backward products through the
+ * layout flags. Either operand may be given transposed:
+ *   a_mn_major = 0: a[m * lda + k]      1: a[k * lda + m]
+ *   b_mn_major = 1: b[k * ldb + n]      0: b[n * ldb + k]        c[m * ldc + n]
+ * ws: lce_matmul_workspace_bytes() bytes (0 unless K is split). */
+size_t lce_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype, unsigned flags);
+int lce_matmul(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int a_mn_major,
+               int64_t lda, int b_mn_major, int64_t ldb, int64_t ldc, int dtype, void* ws, size_t ws_bytes,
+               unsigned flags, void* stream);
 
 /* ---- test hook -------------------------------------------------------------------------------
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,

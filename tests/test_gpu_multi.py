@@ -24,8 +24,9 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, results) -> None:
+def _worker(rank: int, world: int, port: int, results, dx_reduce: str = "p2p") -> None:
     sys.path.insert(0, str(ROOT))
+    os.environ["HELION_B200_DX_REDUCE"] = dx_reduce
     try:
         import torch.distributed as dist
 
@@ -48,9 +49,11 @@ def _worker(rank: int, world: int, port: int, results) -> None:
             xs = d["hidden"].to(dev).requires_grad_(True)
             w_loc, start = parallel.shard_weight(d["weight"].to(dev), dist.group.WORLD)
             w_loc.requires_grad_(True)
-            loss = ops.linear_cross_entropy(xs, w_loc, t, reduction=red, process_group=dist.group.WORLD,
-                                            vocab_start=start)
-            loss.backward(go)
+            for _ in range(2):  # twice: the peer buffers of the first step are reused by the second
+                xs.grad = w_loc.grad = None
+                loss = ops.linear_cross_entropy(xs, w_loc, t, reduction=red, process_group=dist.group.WORLD,
+                                                vocab_start=start)
+                loss.backward(go)
             torch.cuda.synchronize()
             assert abs(float(loss) - float(ref)) <= 1e-6 * abs(float(ref)), (float(loss), float(ref))
             edx = float((xs.grad.float() - x.grad.float()).abs().max() / x.grad.float().abs().max())
@@ -70,14 +73,15 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         results[rank] = "error: " + traceback.format_exc(limit=4)
 
 
+@pytest.mark.parametrize("dx_reduce", ["p2p", "nccl"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_vocab_parallel_matches_single_gpu(world):
+def test_vocab_parallel_matches_single_gpu(world, dx_reduce):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, results, dx_reduce)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

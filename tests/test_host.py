@@ -121,7 +121,7 @@ def _fake_tritium():
         mod.linear_cross_entropy_backward = lambda *a: "reference backward"
         mod.cross_entropy = lambda *a: "reference plain forward"
         mod.cross_entropy_backward = lambda *a: "reference plain backward"
-        mod.matmul = lambda *a: "another op"
+        mod.rmsnorm = lambda *a: "another op"
     root.ops = sub
     # on tritium.ops the attribute `cross_entropy` is the function (it shadows the submodule)
     for mod in (root, sub, leaf):
@@ -135,13 +135,13 @@ def test_install_rebinds_all_three_modules_and_uninstall_restores():
     root, sub, leaf = _fake_tritium()
     try:
         rebound = install(root)
-        assert len(rebound) == 12
+        assert len(rebound) == 12  # (the fake package has no matmul module)
         for mod in (root, sub, leaf):
             assert mod.linear_cross_entropy is ops.linear_cross_entropy
             assert mod.linear_cross_entropy_backward is ops.linear_cross_entropy_backward
             assert mod.cross_entropy is ce_ops.cross_entropy
             assert mod.cross_entropy_backward is ce_ops.cross_entropy_backward
-            assert mod.matmul() == "another op"  # everything else is left alone
+            assert mod.rmsnorm() == "another op"  # everything else is left alone
         install(root)  # idempotent: the saved originals are not overwritten by our own functions
         uninstall(root)
         for mod in (root, sub, leaf):
@@ -215,7 +215,7 @@ def test_null_pointers_and_bad_enums_are_argument_errors():
     L = _lib.lib()
     assert L.lce_forward_stats(None, None, None, 1, 8, 8, 8, 0, 0, None, None, 0, 0, None) == 1
     assert L.lce_forward_stats(None, None, None, 1, 8, 8, 8, 0, 7, None, None, 0, 0, None) == 1
-    assert L.lce_backward(None, None, None, 1, None, None, 8, 8, 8, 0, 0, -100, 9, None, None, None, 0, 0, 0, None, None) == 1
+    assert L.lce_backward(None, None, None, 1, None, None, 8, 8, 8, 0, 0, -100, 9, None, None, None, 0, 0, 0, None, None, None) == 1
     plan = (ctypes.c_int64 * 4)()
     assert L.lce_backward_plan(8192, 4096, 128256, 0, 0, 0, None, None, plan) == 0
     assert list(plan) == [8192, 16384, 1, 8]  # Llama-3 head: all rows, 8 vocabulary bands of 16384 columns
