@@ -60,6 +60,34 @@ __device__ __forceinline__ void ce_unpack_one(const uint4& raw, long long col0, 
     for (int j = 0; j < VEC; ++j) v[j] = (c + j < V) ? Cvt<T>::to_f(tmp[j]) : fill;
 }
 
+// Folds PER logits into a running (max, sum-exp). Four independent chains for the max and for the sum
+// (the serial versions stall on FMNMX / FADD latency with this few warps per SM); the order of the
+// additions is fixed, so the result is the same on every run.
+template <int PER>
+__device__ __forceinline__ void ce_fold(const float (&v)[PER], float& m, float& s) {
+    static_assert(PER % 4 == 0, "four chains");
+    float m0 = v[0], m1 = v[1], m2 = v[2], m3 = v[3];
+#pragma unroll
+    for (int j = 4; j < PER; j += 4) {
+        m0 = fmaxf(m0, v[j]);
+        m1 = fmaxf(m1, v[j + 1]);
+        m2 = fmaxf(m2, v[j + 2]);
+        m3 = fmaxf(m3, v[j + 3]);
+    }
+    const float nm = fmaxf(m, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+    const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j += 4) {
+        a0 += ptx::ex2(fmaf(v[j], kLog2e, -nm2));
+        a1 += ptx::ex2(fmaf(v[j + 1], kLog2e, -nm2));
+        a2 += ptx::ex2(fmaf(v[j + 2], kLog2e, -nm2));
+        a3 += ptx::ex2(fmaf(v[j + 3], kLog2e, -nm2));
+    }
+    s = s * ptx::ex2(fmaf(m, kLog2e, -nm2)) + ((a0 + a1) + (a2 + a3));
+    m = nm;
+}
+
 // Index (0 .. kPerThread-1) of the register of THIS thread that holds column `target`, or -1.
 template <class T>
 __device__ __forceinline__ int ce_target_slot(long long col0, long long target) {
@@ -107,16 +135,7 @@ ce_row_stats_kernel(const T* __restrict__ logits, const void* tgt, int tgt_i64, 
 #pragma unroll
             for (int j = 0; j < VEC; ++j) v[g * VEC + j] = part[j];
         }
-        float cm = v[0];
-#pragma unroll
-        for (int j = 1; j < PER; ++j) cm = fmaxf(cm, v[j]);
-        const float nm = fmaxf(m, cm);
-        const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
-        float acc = 0.f;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) acc += ptx::ex2(fmaf(v[j], kLog2e, -nm2));
-        s = s * ptx::ex2(fmaf(m, kLog2e, -nm2)) + acc;
-        m = nm;
+        ce_fold<PER>(v, m, s);
         const int slot = ce_target_slot<T>(col0, target);
         if (slot >= 0) {  // at most one thread of the CTA, in one chunk
 #pragma unroll
