@@ -56,8 +56,13 @@ __device__ __forceinline__ void ce_unpack_one(const uint4& raw, long long col0, 
     const long long c = col0 + (static_cast<long long>(g) * kCeThreads + threadIdx.x) * VEC;
     alignas(16) T tmp[VEC];
     *reinterpret_cast<uint4*>(tmp) = raw;
+    if (c + VEC <= V) {  // whole vector in range (one test per vector, not per element)
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) v[j] = (c + j < V) ? Cvt<T>::to_f(tmp[j]) : fill;
+        for (int j = 0; j < VEC; ++j) v[j] = Cvt<T>::to_f(tmp[j]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = (c + j < V) ? Cvt<T>::to_f(tmp[j]) : fill;
+    }
 }
 
 // Folds PER logits into a running (max, sum-exp). Four independent chains for the max and for the sum
