@@ -133,6 +133,9 @@ def build_workload(name: str):
 
     if name.startswith("sweep-"):
         return inputs.sweep_config(int(name.split("-", 1)[1]))
+    if name.startswith("shape-"):  # shape-<tokens>x<hidden>x<vocab>: uniform targets, nothing ignored
+        n, h, v = (int(p) for p in name.split("-", 1)[1].split("x"))
+        return inputs.HeadConfig(name, 1, n, h, v)
     return inputs.CONFIGS[name]
 
 

@@ -8,6 +8,8 @@
 // Row reductions are therefore thread-local: no shuffles, no shared memory.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_tc.cuh"
 
 namespace lce {
@@ -266,6 +268,33 @@ struct EpiStore {
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     sp[i * kBM] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                return;
+            }
+        }
+        if constexpr (std::is_same<T, float>::value) {
+            if (p.peer_world > 0 && tc.stage != nullptr) {
+                // Peer rows leave as whole 128-byte lines: the warp re-shapes its 32 x 32 chunk through
+                // shared memory so that 8 lanes cover one row (4 columns each) instead of every lane
+                // sending 16 bytes of a different row - NVLink carries few large writes far better than
+                // many small ones. All 32 lanes take part; rows / columns out of range are skipped.
+                const int lane = tc.row_in_tile & 31;
+                float* sm = tc.stage;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sm[lane * 33 + j] = v[j];
+                __syncwarp();
+                const int row_base = st.row - lane;
+                const int c4 = (lane & 7) * 4;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int r = it * 4 + (lane >> 3);
+                    float* dst = reinterpret_cast<float*>(
+                        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(st.dst), r));
+                    if (row_base + r < p.rows && gcol0 + c4 + 4 <= p.cols) {
+                        const float* src = sm + r * 33 + c4;
+                        *reinterpret_cast<float4*>(dst + gcol0 + c4) = make_float4(src[0], src[1], src[2], src[3]);
+                    }
+                }
+                __syncwarp();
                 return;
             }
         }

@@ -85,7 +85,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
             __syncthreads();
         }
 
-        TileCtx tc{m_tile, n_tile, n_tiles, t, kSimtBN, 0};
+        TileCtx tc{m_tile, n_tile, n_tiles, t, kSimtBN, 0, nullptr};
         typename Epi::State st;
         Epi::begin(st, ep, tc);
         Epi::chunk(st, ep, tc, 0, acc);

@@ -55,7 +55,10 @@ struct TileCtx {
     int row_in_tile;  // 0..127, the row this thread owns
     int bn;           // tile width in columns
     int k_slice;      // which slice of the contraction this tile holds (0 unless K is split)
+    float* stage;     // this warp's 32 x 33 floats of shared memory for re-shaping a chunk, or nullptr
 };
+
+constexpr int kStageFloatsPerWarp = 32 * 33;
 
 template <int BN, int STAGES, int CG>
 struct GemmSmem {
@@ -64,8 +67,9 @@ struct GemmSmem {
     static constexpr int kBBytes = kBRows * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 256;
+    static constexpr int kEpiStageBytes = 4 * kStageFloatsPerWarp * 4;  // one re-shaping area per epilogue warp
     // 1024 bytes of slack so the ring can be aligned to the swizzle atom by hand
-    static constexpr int kTotalBytes = STAGES * kStageBytes + kBarrierBytes + 1024;
+    static constexpr int kTotalBytes = STAGES * kStageBytes + kBarrierBytes + kEpiStageBytes + 1024;
 };
 
 // m_fastest: consecutive tile indices walk down the rows first (CTAs running together share a
@@ -295,7 +299,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
             const uint32_t buf = local_tile & 1u;
             const uint32_t buf_phase = (local_tile >> 1) & 1u;
-            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN, work / total_units};
+            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN, work / total_units,
+                       reinterpret_cast<float*>(gen_bar_base + S::kBarrierBytes) + (warp - 2) * kStageFloatsPerWarp};
             Epi::begin(st, ep, tc);  // global loads for this row overlap the wait below
             if (!ptx::mbar_wait(tfull_bar(buf), buf_phase, abort_flag)) {
                 ok = false;

@@ -307,10 +307,10 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     ws = _workspace(L.lce_backward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags, block), dev)
 
     # Sharded: two ways to sum the partial dX over the group.
-    #  "p2p" (default): the dX GEMM's epilogue stores finished rows straight into the owning rank's staging
-    #        buffer over NVLink (reduce-scatter inside the GEMM); a small kernel then sums and all-gathers.
-    #  "nccl": fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library signals
-    #        the chunk final, while the remaining dW GEMMs run on the main stream.
+    #  "nccl" (default): fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library
+    #        signals the chunk final, while the remaining dW GEMMs run on the main stream.
+    #  "p2p": the dX GEMM's epilogue stores finished rows straight into the owning rank's staging buffer
+    #        over NVLink (reduce-scatter inside the GEMM); a small kernel then sums and all-gathers.
     events, event_array, chunk_rows, scatter, peers = None, None, n_rows, None, None
     if sharded and dx is not None:
         plan = (ctypes.c_int64 * 4)()
@@ -344,7 +344,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
 
 
 def _dx_reduce_mode() -> str:
-    return os.environ.get("HELION_B200_DX_REDUCE", "p2p")
+    return os.environ.get("HELION_B200_DX_REDUCE", "nccl")
 
 
 def _finish_peer_reduce(peers, events, n_rows: int, hidden_size: int, dtype: int, dev: torch.device) -> torch.Tensor:
