@@ -307,10 +307,11 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     ws = _workspace(L.lce_backward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags, block), dev)
 
     # Sharded: two ways to sum the partial dX over the group.
-    #  "nccl" (default): fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library
-    #        signals the chunk final, while the remaining dW GEMMs run on the main stream.
-    #  "p2p": the dX GEMM's epilogue stores finished rows straight into the owning rank's staging buffer
-    #        over NVLink (reduce-scatter inside the GEMM); a small kernel then sums and all-gathers.
+    #  "p2p" (default): the dX GEMM's epilogue stores finished rows straight into the owning rank's staging
+    #        buffer over NVLink (reduce-scatter inside the GEMM); a small kernel then sums and all-gathers.
+    #        Falls back to "nccl" for the whole group if peer-mapped memory cannot be set up.
+    #  "nccl": fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library signals
+    #        the chunk final, while the remaining dW GEMMs run on the main stream.
     events, event_array, chunk_rows, scatter, peers = None, None, n_rows, None, None
     if sharded and dx is not None:
         plan = (ctypes.c_int64 * 4)()
@@ -321,6 +322,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
         event_array = (ctypes.c_void_p * n_chunks)(*[e.cuda_event for e in events])
         if _dx_reduce_mode() == "p2p" and hidden_size % 4 == 0 and world <= 8:
             peers = parallel.peer_buffers(process_group, n_rows, hidden_size, hidden2d.dtype, dev)
+        if peers is not None:
             scatter = _lib.PeerScatter()
             for k, ptr in enumerate(peers.staging_ptrs):
                 scatter.staging[k] = ptr
@@ -344,7 +346,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
 
 
 def _dx_reduce_mode() -> str:
-    return os.environ.get("HELION_B200_DX_REDUCE", "nccl")
+    return os.environ.get("HELION_B200_DX_REDUCE", "p2p")
 
 
 def _finish_peer_reduce(peers, events, n_rows: int, hidden_size: int, dtype: int, dev: torch.device) -> torch.Tensor:

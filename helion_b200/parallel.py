@@ -143,11 +143,23 @@ class PeerBuffers:
         dist.all_reduce(self.flag, group=self.group)
 
 
-_peer_buffers: dict[tuple, PeerBuffers] = {}
+_peer_buffers: dict[tuple, PeerBuffers | None] = {}
 
 
-def peer_buffers(process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype, device: torch.device) -> PeerBuffers:
+def peer_buffers(process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype,
+                 device: torch.device) -> PeerBuffers | None:
+    """The cached peer buffers of this problem, or None if peer-mapped memory cannot be set up on this
+    machine. The decision is collective (a MIN all-reduce over the group), so either every rank takes the
+    fused path or every rank takes the NCCL path."""
     key = (id(process_group), n_rows, hidden, dtype, device.index)
     if key not in _peer_buffers:
-        _peer_buffers[key] = PeerBuffers(process_group, n_rows, hidden, dtype, device)
+        import torch.distributed as dist
+
+        try:
+            bufs = PeerBuffers(process_group, n_rows, hidden, dtype, device)
+        except Exception:  # noqa: BLE001 - e.g. no peer access between these GPUs
+            bufs = None
+        agreed = torch.tensor([1.0 if bufs is not None else 0.0], device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=process_group)
+        _peer_buffers[key] = bufs if float(agreed.item()) == 1.0 else None
     return _peer_buffers[key]
