@@ -72,16 +72,30 @@ struct GemmSmem {
     static constexpr int kTotalBytes = STAGES * kStageBytes + kBarrierBytes + kEpiStageBytes + 1024;
 };
 
-// m_fastest: consecutive tile indices walk down the rows first (CTAs running together share a
-// B panel); otherwise they walk across the columns first (CTAs share an A panel).
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int m_fastest,
-                                            int& m_tile, int& n_tile) {
-    if (m_fastest) {
-        m_tile = tile % m_tiles;
-        n_tile = tile / m_tiles;
+// Tile order. The tile grid (m_units x n_tiles) is cut into bands along one dimension; inside a band
+// consecutive tile indices walk the banded dimension first. CTAs that run together therefore share
+// the panels of the OTHER operand, and the band's own panels (band width x K) are what must stay
+// resident in L2 while the other operand streams through once per band.
+//   raster > 0:  bands of `raster` row units (m fastest inside a band)   - X.W^T passes: the band of X
+//                stays in L2 while W streams; raster >= m_units is plain "rows first".
+//   raster < 0:  bands of `-raster` tile columns (n fastest inside)      - dW / dX passes.
+__device__ __forceinline__ void tile_coords(int tile, int m_units, int n_tiles, int raster,
+                                            int& m_unit, int& n_tile) {
+    if (raster > 0) {
+        const int band_tiles = raster * n_tiles;
+        const int band = tile / band_tiles;
+        const int r = tile - band * band_tiles;
+        const int w = min(raster, m_units - band * raster);
+        n_tile = r / w;
+        m_unit = band * raster + (r - n_tile * w);
     } else {
-        n_tile = tile % n_tiles;
-        m_tile = tile / n_tiles;
+        const int wb = -raster;
+        const int band_tiles = wb * m_units;
+        const int band = tile / band_tiles;
+        const int r = tile - band * band_tiles;
+        const int w = min(wb, n_tiles - band * wb);
+        m_unit = r / w;
+        n_tile = band * wb + (r - m_unit * w);
     }
 }
 
@@ -95,7 +109,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               int m_tiles, int n_tiles, int k_blocks, int k_splits, int m_fastest,
+               int m_tiles, int n_tiles, int k_blocks, int k_splits, int raster, int l2_hints,
                const typename Epi::Params ep, int* __restrict__ status) {
     using S = GemmSmem<BN, STAGES, CG>;
     static_assert(CG == 1 || CG == 2, "cta group");
@@ -166,9 +180,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t issued = 0;
             bool ok = true;
             const uint32_t leader_full0 = kPair ? ptx::map_to_cta(full_bar(0), 0) : 0u;
+            // l2_hints: eviction priority of operand A in bits 0-1, of operand B in bits 2-3
+            const uint64_t policy_a = ptx::make_l2_policy(l2_hints & 3);
+            const uint64_t policy_b = ptx::make_l2_policy((l2_hints >> 2) & 3);
             for (int work = unit0; work < total_work && ok; work += unit_step) {
                 int m_unit, n_tile;
-                tile_coords(work % total_units, m_units, n_tiles, m_fastest, m_unit, n_tile);
+                tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
                 const int kb_begin = (work / total_units) * kb_per_slice;
                 const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
                 const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
@@ -185,8 +202,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // the barrier the MMA issuer waits on: our own, or the leader's for a pair
                     const uint32_t fb = kPair ? leader_full0 + 8u * stage : full_bar(stage);
                     auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
-                        if constexpr (kPair) ptx::tma_load_2d_pair(dst, tm, fb, x, y);
-                        else ptx::tma_load_2d(dst, tm, fb, x, y);
+                        const uint64_t policy = (tm == &tmA) ? policy_a : policy_b;
+                        if constexpr (kPair) ptx::tma_load_2d_pair_hint(dst, tm, fb, x, y, policy);
+                        else ptx::tma_load_2d_hint(dst, tm, fb, x, y, policy);
                     };
                     // bytes of the whole group's copies for this stage, announced by the leader only
                     if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes * CG);
@@ -295,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         typename Epi::State st;
         for (int work = unit0; work < total_work && ok; work += unit_step, ++local_tile) {
             int m_unit, n_tile;
-            tile_coords(work % total_units, m_units, n_tiles, m_fastest, m_unit, n_tile);
+            tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
             const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
             const uint32_t buf = local_tile & 1u;
             const uint32_t buf_phase = (local_tile >> 1) & 1u;

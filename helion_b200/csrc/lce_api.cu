@@ -4,6 +4,7 @@
 #include <cudaTypedefs.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -103,6 +104,16 @@ struct Mat {
 template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
                  int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream) {
+    // Band the tile order so that the panels which co-running CTAs do NOT share stay resident in L2:
+    // about 32 MB of them (the two L2 partitions of 63 MB each also hold the streaming operand).
+    static const long long kBandBytes = [] {  // HELION_B200_BAND_MB overrides (tuning knob)
+        const char* e = getenv("HELION_B200_BAND_MB");
+        return (e && atoll(e) > 0 ? atoll(e) : 32ll) << 20;
+    }();
+    static const int kHintMode = [] {  // 0 none, 1 resident operand evict_last + streaming evict_first, 2 evict_last only
+        const char* e = getenv("HELION_B200_L2_HINTS");
+        return e ? atoi(e) : 2;
+    }();
     constexpr int kStages = CG == 2 ? kStages2 : kStages1;
     const int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
     CUtensorMap tma, tmb;
@@ -143,9 +154,22 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CG > 1 ? 1 : 0;
+    // the banded operand is re-read by every tile of the band: keep it; the other one streams
+    const int stream_hint = kHintMode == 1 ? ptx::kL2EvictFirst : ptx::kL2Normal;
+    const int l2_hints = kHintMode == 0 ? 0 : (m_fastest ? (ptx::kL2EvictLast | (stream_hint << 2))
+                                                          : (stream_hint | (ptx::kL2EvictLast << 2)));
+    int raster;
+    if (m_fastest) {  // bands of row units: rows fastest inside
+        long long wb = kBandBytes / (static_cast<long long>(CG) * kBM * K * 2);
+        const long long m_units = cdiv(m_tiles, CG);
+        raster = static_cast<int>(wb < 1 ? 1 : (wb > m_units ? m_units : wb));
+    } else {  // bands of tile columns: columns fastest inside
+        long long wb = kBandBytes / (static_cast<long long>(kBN) * K * 2);
+        raster = -static_cast<int>(wb < 1 ? 1 : (wb > n_tiles ? n_tiles : wb));
+    }
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
-                                               m_fastest, ep, d.status_ptr);
+                                               raster, l2_hints, ep, d.status_ptr);
     LCE_COUNT_LAUNCH();
     return err == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }

@@ -131,6 +131,37 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// L2 eviction-priority policies for TMA loads. An operand that every tile of a band re-reads is loaded
+// evict_last so that the operand streaming past it (evict_first: read by the tiles running right now,
+// then dead) cannot push it out.
+enum L2Hint { kL2Normal = 0, kL2EvictFirst = 1, kL2EvictLast = 2 };
+
+__device__ __forceinline__ uint64_t make_l2_policy(int hint) {
+    uint64_t p;
+    if (hint == kL2EvictFirst) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    else if (hint == kL2EvictLast) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const CUtensorMap* tm, uint32_t bar,
+                                                 int32_t x, int32_t y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar,
+                                                      int32_t x, int32_t y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
 // ---------------------------------------------------------------------------------------------
