@@ -33,6 +33,15 @@ METRIC = "linear_ce_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
 
+def load_traffic(workload: str, world: int):
+    """DRAM bytes per launch of the forward GEMM from the committed ncu capture of this workload
+    (profiles/dram_traffic.json: dram__bytes_read.sum + dram__bytes_write.sum), or None."""
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if not path.exists() or world != 1:
+        return None
+    return json.loads(path.read_text()).get(workload, {}).get("forward_gemm_bytes_per_launch")
+
+
 def load_peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -357,10 +366,14 @@ def run_ours(args) -> None:
         "step_frac_of_peak": {"burst_%g" % peaks["burst"]: tf_step / peaks["burst"],
                               "sustained_%g" % peaks["sustained"]: tf_step / peaks["sustained"],
                               "nominal_2250": tf_step / 2250.0},
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<EpiStats> (forward logits + softmax statistics)",
+        "roofline": {"bound": "tensor",
+                     "kernel": "gemm_tc_kernel<256,6,2,K,K,bf16,EpiStats> (forward logits + softmax statistics; "
+                               "timed through lce_forward_stats, which also runs the sub-1% merge kernel)",
                      "achieved": tf_fwd, "peak": peaks["burst"], "peak_source": peaks["source"] + " burst",
                      "unit": "TFLOP/s", "frac": tf_fwd / peaks["burst"], "ms_per_launch": ms_fwd,
-                     "flops_per_launch": flops_fwd, "traffic": None},
+                     "flops_per_launch": flops_fwd, "traffic": load_traffic(cfg.name, world),
+                     "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
+                     "algorithmic_bytes_per_launch": (n * h + v_loc * h) * 2 + (v_loc + 255) // 256 * 3 * n * 4},
         "e2e": {"value": n / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + t_host.numel() * t_host.element_size(),
                 "d2h_bytes_per_step": 4},
