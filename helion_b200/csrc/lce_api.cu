@@ -292,7 +292,7 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiStats>(d, a, b, N, V, H, /*m_fastest=*/1, ep, stream);
+            rc = launch_tc<false, false, kBf16, EpiStats>(d, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream);
         } else {
             rc = LCE_ERR_ARG;
         }
