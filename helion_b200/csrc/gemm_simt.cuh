@@ -29,13 +29,21 @@ struct SimtOperand {
 
 template <class T, class Epi>
 __global__ void __launch_bounds__(kSimtThreads)
-gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_tiles,
+gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_tiles, int k_splits,
                  const typename Epi::Params ep) {
     __shared__ float As[kSimtBK][kBM + 1];
     __shared__ __align__(16) float Bs[kSimtBK][kSimtBN];
 
     const int t = threadIdx.x;
-    for (int tile = blockIdx.x; tile < m_tiles * n_tiles; tile += gridDim.x) {
+    // k_splits > 1: work item = (tile, slice of the contraction); the epilogue stores slices side by side
+    // (kStoreSlice) and splitk_reduce_kernel adds them in slice order.
+    const int total_tiles = m_tiles * n_tiles;
+    const int k_per_slice = ((K + k_splits - 1) / k_splits + kSimtBK - 1) / kSimtBK * kSimtBK;
+    for (int work = blockIdx.x; work < total_tiles * k_splits; work += gridDim.x) {
+        const int tile = work % total_tiles;
+        const int k_slice = work / total_tiles;
+        const int k_begin = k_slice * k_per_slice;
+        const int k_end = min(K, k_begin + k_per_slice);
         const int n_tile = tile % n_tiles;
         const int m_tile = tile / n_tiles;
         const int m0 = m_tile * kBM;
@@ -45,7 +53,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = 0.f;
 
-        for (int k0 = 0; k0 < K; k0 += kSimtBK) {
+        for (int k0 = k_begin; k0 < k_end; k0 += kSimtBK) {
             // A tile: 128 x 16. Walk the contiguous direction with consecutive threads.
 #pragma unroll
             for (int i = 0; i < (kBM * kSimtBK) / kSimtThreads; ++i) {
@@ -54,7 +62,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
                 if (A.stride_k == 1) { k = idx % kSimtBK; m = idx / kSimtBK; }
                 else { m = idx % kBM; k = idx / kBM; }
                 float val = 0.f;
-                if (m0 + m < A.extent_mn && k0 + k < K)
+                if (m0 + m < A.extent_mn && k0 + k < k_end)
                     val = Cvt<T>::to_f(A.ptr[(long long)(m0 + m) * A.stride_mn + (long long)(k0 + k) * A.stride_k]);
                 As[k][m] = val;
             }
@@ -65,7 +73,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
                 if (B.stride_k == 1) { k = idx % kSimtBK; n = idx / kSimtBK; }
                 else { n = idx % kSimtBN; k = idx / kSimtBN; }
                 float val = 0.f;
-                if (n0 + n < B.extent_mn && k0 + k < K)
+                if (n0 + n < B.extent_mn && k0 + k < k_end)
                     val = Cvt<T>::to_f(B.ptr[(long long)(n0 + n) * B.stride_mn + (long long)(k0 + k) * B.stride_k]);
                 Bs[k][n] = val;
             }
@@ -85,7 +93,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
             __syncthreads();
         }
 
-        TileCtx tc{m_tile, n_tile, n_tiles, t, kSimtBN, 0, nullptr};
+        TileCtx tc{m_tile, n_tile, n_tiles, t, kSimtBN, k_slice, nullptr};
         typename Epi::State st;
         Epi::begin(st, ep, tc);
         Epi::chunk(st, ep, tc, 0, acc);

@@ -189,6 +189,16 @@ int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long
     return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
 }
 
+// The same for the CUDA-core GEMM (128 x 32 tiles, up to four CTAs per SM worth of work items).
+int choose_k_splits_simt(long long M, long long Nn, long long K) {
+    const long long units = cdiv(M, kBM) * cdiv(Nn, kSimtBN);
+    if (units == 0 || units * 2 > 592) return 1;
+    long long s = 592 / units;
+    if (s > 32) s = 32;
+    while (s > 1 && (K / s < 64 || (s - 1) * (cdiv(cdiv(K, s), kSimtBK) * kSimtBK) >= K)) --s;
+    return static_cast<int>(s);
+}
+
 // How many slices to cut the contraction of an M x Nn x K GEMM into so that a problem with few output
 // tiles still fills the GPU (the deterministic split-K: slices are added in slice order afterwards).
 // Uses a fixed SM count so that workspace sizes do not depend on the device.
@@ -205,7 +215,7 @@ int choose_k_splits(long long M, long long Nn, long long K) {
 
 template <class T, class Epi>
 int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool b_mn, long long M,
-                long long Nn, long long K, const typename Epi::Params& ep, cudaStream_t stream) {
+                long long Nn, long long K, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1) {
     SimtOperand<T> A, B;
     A.ptr = static_cast<const T*>(a.ptr);
     A.stride_mn = a_mn ? 1 : a.pitch_elems;
@@ -219,9 +229,10 @@ int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool
     if (m_tiles * n_tiles > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
     if (m_tiles * n_tiles == 0 || K == 0) return LCE_OK;
     const long long cap = static_cast<long long>(d.sm_count) * 16;
-    const int grid = static_cast<int>(m_tiles * n_tiles < cap ? m_tiles * n_tiles : cap);
+    const long long work = m_tiles * n_tiles * k_splits;
+    const int grid = static_cast<int>(work < cap ? work : cap);
     gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(
-        A, B, static_cast<int>(K), static_cast<int>(m_tiles), static_cast<int>(n_tiles), ep);
+        A, B, static_cast<int>(K), static_cast<int>(m_tiles), static_cast<int>(n_tiles), k_splits, ep);
     LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
@@ -330,6 +341,7 @@ struct BwdPlan {
     long long dw_band_scratch_floats;
     int dx_splits;               // k slices of the dX GEMM when one band covers the vocabulary
     long long dx_slab_floats;    // fp32 scratch of one dX row chunk (one slice)
+    int dw_splits;               // k slices of the dW GEMM when one chunk covers all rows (short vocabulary)
 };
 
 BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use_tc, unsigned flags,
@@ -380,13 +392,16 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     off += align_up(static_cast<size_t>(p.nr) * p.ldg * e, 256);
     p.off_dx_scratch = off;
     p.dx_slab_floats = cdiv(p.nr, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
-    p.dx_splits = (use_tc && need_dx && p.n_cblk == 1) ? choose_k_splits(p.nr, H, p.nc) : 1;
+    p.dx_splits = (need_dx && p.n_cblk == 1) ? (use_tc ? choose_k_splits(p.nr, H, p.nc) : choose_k_splits_simt(p.nr, H, p.nc)) : 1;
+    p.dw_splits = (need_dw && p.n_rblk == 1) ? (use_tc ? choose_k_splits(p.nc, H, p.nr) : choose_k_splits_simt(p.nc, H, p.nr)) : 1;
     if (need_dx && (p.n_cblk > 1 || p.dx_splits > 1))
         off += align_up(static_cast<size_t>(p.dx_splits) * p.dx_slab_floats * sizeof(float), 256);
     p.off_dw_scratch = off;
     p.dw_band_scratch_floats = cdiv(p.nc, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
     if (need_dw && p.n_rblk > 1)
         off += align_up(static_cast<size_t>(p.n_cblk) * p.dw_band_scratch_floats * sizeof(float), 256);
+    else if (need_dw && p.dw_splits > 1)  // slices of one band at a time
+        off += align_up(static_cast<size_t>(p.dw_splits) * p.dw_band_scratch_floats * sizeof(float), 256);
     p.total = off;
     return p;
 }
@@ -470,15 +485,16 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                         rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, gm, b, nr, H, nc, 0, ep, stream, splits);
                     else rc = LCE_ERR_ARG;
                 } else {
-                    rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream);
+                    rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream, splits);
                 }
                 if (rc) return rc;
                 if (splits > 1) {
-                    const int m_tiles = static_cast<int>(cdiv(nr, kBM)), n_tiles = static_cast<int>(cdiv(H, kBN));
-                    const long long quads = static_cast<long long>(m_tiles) * n_tiles * (kBN / 4) * kBM;
+                    const int bn = static_cast<int>(p.bn);
+                    const int m_tiles = static_cast<int>(cdiv(nr, kBM)), n_tiles = static_cast<int>(cdiv(H, bn));
+                    const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
                     const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
                     splitk_reduce_kernel<TDx><<<blocks, 256, 0, stream>>>(
-                        ep.scratch, splits, p.dx_slab_floats, m_tiles, n_tiles, kBN, static_cast<int>(nr),
+                        ep.scratch, splits, p.dx_slab_floats, m_tiles, n_tiles, bn, static_cast<int>(nr),
                         static_cast<int>(H), ep.out, H);
                     LCE_COUNT_LAUNCH();
                     if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
@@ -498,17 +514,34 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 ep.cols = static_cast<int>(H);
                 ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch) + cb * p.dw_band_scratch_floats;
                 ep.mode = store_mode(rb, p.n_rblk);
-                ep.slab_floats = 0;
+                ep.slab_floats = p.dw_band_scratch_floats;
                 ep.peer_world = 0;
                 const Mat b{xp + r0 * H, nr, H, H};
+                // short vocabulary block (few output tiles): cut the token contraction into slices
+                const int wsplits = (p.dw_splits > 1 && p.n_rblk == 1 && nc == p.nc) ? p.dw_splits : 1;
+                if (wsplits > 1) {
+                    ep.mode = kStoreSlice;
+                    ep.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch);
+                }
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream);
+                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream, wsplits);
                     else rc = LCE_ERR_ARG;
                 } else {
-                    rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream);
+                    rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream, wsplits);
                 }
                 if (rc) return rc;
+                if (wsplits > 1) {
+                    const int bn = static_cast<int>(p.bn);
+                    const int m_tiles = static_cast<int>(cdiv(nc, kBM)), n_tiles = static_cast<int>(cdiv(H, bn));
+                    const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
+                    const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
+                    splitk_reduce_kernel<T><<<blocks, 256, 0, stream>>>(
+                        ep.scratch, wsplits, p.dw_band_scratch_floats, m_tiles, n_tiles, bn, static_cast<int>(nc),
+                        static_cast<int>(H), ep.out, H);
+                    LCE_COUNT_LAUNCH();
+                    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+                }
             }
         }
     }

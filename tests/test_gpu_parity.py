@@ -185,7 +185,8 @@ def test_scaled_configurations(name, shape, force, monkeypatch):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(1, 64, 65), (2, 8, 3), (127, 72, 129), (129, 136, 257), (130, 70, 300),
                                    (257, 200, 1000), (300, 768, 16064),
-                                   (128, 512, 9000), (512, 1024, 20000)])  # the last two split the dX contraction
+                                   (128, 512, 9000), (512, 1024, 20000),  # these two split the dX contraction
+                                   (4096, 256, 65), (2048, 72, 130)])  # and these the dW contraction (char-LM heads)
 def test_ragged_shapes(shape, dtype):
     n, h, v = shape
     g = torch.Generator().manual_seed(n * 7 + v)
