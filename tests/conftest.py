@@ -23,3 +23,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _seed_torch():
+    """The reference's tests draw unseeded random inputs; here every test starts from the same seed so
+    that a pass or a failure is reproducible."""
+    import torch
+
+    torch.manual_seed(20240607)
