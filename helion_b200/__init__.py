@@ -8,11 +8,15 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 from .ce_ops import cross_entropy, cross_entropy_backward
 from .install import install, uninstall
 from .matmul_ops import matmul, matmul_vec
+from .optim_ops import adamw_step, clip_grad_norm, grad_sumsq
 from .ops import linear_cross_entropy, linear_cross_entropy_backward
 
 __all__ = [
+    "adamw_step",
+    "clip_grad_norm",
     "cross_entropy",
     "cross_entropy_backward",
+    "grad_sumsq",
     "install",
     "linear_cross_entropy",
     "linear_cross_entropy_backward",

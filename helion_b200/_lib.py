@@ -50,6 +50,10 @@ SIGNATURES = {
     "lce_matmul_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
     "lce_matmul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int, c_int64,
                            c_int64, c_int, c_void_p, c_size_t, c_uint, c_void_p]),
+    "lce_adamw_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, ctypes.c_float, ctypes.c_float,
+                               ctypes.c_float, ctypes.c_float, ctypes.c_float, c_int64, c_void_p, c_void_p]),
+    "lce_sumsq_workspace_bytes": (c_size_t, []),
+    "lce_sumsq": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                c_uint, c_void_p]),
 }

@@ -4,6 +4,7 @@
 #include <cudaTypedefs.h>
 
 #include <atomic>
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -12,6 +13,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "ce_kernels.cuh"
+#include "optim_kernels.cuh"
 #include "row_kernels.cuh"
 
 namespace lce {
@@ -1172,6 +1174,69 @@ int lce_matmul(const void* a, const void* b, void* c, int64_t M, int64_t N, int6
         case LCE_DTYPE_F16: return matmul_impl<__half>(*d, p, am, a_mn_major, bm, b_mn_major, c, M, N, K, ldc, ws, s);
         default: return matmul_impl<float>(*d, p, am, a_mn_major, bm, b_mn_major, c, M, N, K, ldc, ws, s);
     }
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Consumers of dW: AdamW step and the sum of squares for gradient clipping
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+int lce_adamw_step(void* param, const void* grad, float* exp_avg, float* exp_avg_sq, int64_t n, int dtype, float lr,
+                   float beta1, float beta2, float eps, float weight_decay, int64_t step, const float* grad_scale,
+                   void* stream) {
+    if (n < 0 || step < 1) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if (n == 0) return LCE_OK;
+    if (!param || !grad || !exp_avg || !exp_avg_sq) return LCE_ERR_ARG;
+    if (!aligned16(param) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq)) return LCE_ERR_ALIGN;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    // bias corrections in double, as Python computes them for the reference kernel
+    const float bc1 = static_cast<float>(1.0 - pow(static_cast<double>(beta1), static_cast<double>(step)));
+    const float bc2 = static_cast<float>(1.0 - pow(static_cast<double>(beta2), static_cast<double>(step)));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long vecs = n / (16 / static_cast<long long>(elem_size(dtype))) + 1;
+    const long long want = cdiv(vecs, kOptThreads);  // one 16-byte vector per thread: nothing but loads in flight
+    const int blocks = static_cast<int>(want < 0x7fffffffll ? want : 0x7fffffffll);
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            adamw_step_kernel<__nv_bfloat16><<<blocks, kOptThreads, 0, s>>>(static_cast<__nv_bfloat16*>(param), static_cast<const __nv_bfloat16*>(grad), exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+            break;
+        case LCE_DTYPE_F16:
+            adamw_step_kernel<__half><<<blocks, kOptThreads, 0, s>>>(static_cast<__half*>(param), static_cast<const __half*>(grad), exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+            break;
+        default:
+            adamw_step_kernel<float><<<blocks, kOptThreads, 0, s>>>(static_cast<float*>(param), static_cast<const float*>(grad), exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+    }
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+size_t lce_sumsq_workspace_bytes(void) { return kSumsqBlocks * sizeof(float); }
+
+int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, void* ws, size_t ws_bytes, void* stream) {
+    if (n < 0 || !out) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if (!ws || ws_bytes < kSumsqBlocks * sizeof(float)) return LCE_ERR_WS_TOO_SMALL;
+    if (n > 0 && (!x || !aligned16(x))) return x ? LCE_ERR_ALIGN : LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* partials = static_cast<float*>(ws);
+    switch (dtype) {
+        case LCE_DTYPE_BF16: sumsq_partial_kernel<__nv_bfloat16><<<kSumsqBlocks, kOptThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, partials); break;
+        case LCE_DTYPE_F16: sumsq_partial_kernel<__half><<<kSumsqBlocks, kOptThreads, 0, s>>>(static_cast<const __half*>(x), n, partials); break;
+        default: sumsq_partial_kernel<float><<<kSumsqBlocks, kOptThreads, 0, s>>>(static_cast<const float*>(x), n, partials);
+    }
+    LCE_COUNT_LAUNCH();
+    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    sumsq_final_kernel<<<1, 1024, 0, s>>>(partials, kSumsqBlocks, out, accumulate);
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
 }  // extern "C"

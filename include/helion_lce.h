@@ -208,6 +208,20 @@ int lce_matmul(const void* a, const void* b, void* c, int64_t M, int64_t N, int6
                int64_t lda, int b_mn_major, int64_t ldb, int64_t ldc, int dtype, void* ws, size_t ws_bytes,
                unsigned flags, void* stream);
 
+/* ---- consumers of dW --------------------------------------------------------------------------------
+ * lce_adamw_step replaces the launch of tritium.adamw_step (tritium/ops/adamw.py:21-54, :113-151): in-place
+ * AdamW on `param` (n elements of `dtype`, grad the same dtype) with fp32 moments, same arithmetic in fp32.
+ * grad_scale: NULL, or a device scalar multiplied into the gradient first (the clipping coefficient of
+ * helion.clip_grad_norm, helion/training.py:36-49, applied without a separate pass over the gradients).
+ * lce_sumsq: out (+)= sum of x[i]^2 (fp32, fixed summation order: identical bits from run to run), the
+ * quantity behind clip_grad_norm; ws: lce_sumsq_workspace_bytes(). All pointers 16-byte aligned. */
+int lce_adamw_step(void* param, const void* grad, float* exp_avg, float* exp_avg_sq, int64_t n, int dtype,
+                   float lr, float beta1, float beta2, float eps, float weight_decay, int64_t step,
+                   const float* grad_scale, void* stream);
+size_t lce_sumsq_workspace_bytes(void);
+int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, void* ws, size_t ws_bytes,
+              void* stream);
+
 /* ---- test hook -------------------------------------------------------------------------------
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
  * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b

@@ -228,6 +228,27 @@ def restated_plain_backward(grad_out: torch.Tensor, logits: torch.Tensor, target
 
 
 # ----------------------------------------------------------------------------------------------
+# consumers of dW
+# ----------------------------------------------------------------------------------------------
+def restated_adamw_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, *,
+                        lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                        weight_decay: float = 0.01, step: int = 1, grad_scale: float = 1.0) -> dict:
+    """The reference's AdamW kernel (tritium/ops/adamw.py:36-54) in fp32 torch: returns the new
+    (param in its dtype, exp_avg, exp_avg_sq)."""
+    p = param.detach().float()
+    g = grad.detach().float() * grad_scale
+    # the kernel receives beta1 / beta2 as fp32 arguments and forms (1 - beta) in fp32 (:46-47)
+    b1 = torch.tensor(beta1, dtype=torch.float32)
+    b2 = torch.tensor(beta2, dtype=torch.float32)
+    m = b1 * exp_avg.detach().float() + (1.0 - b1) * g
+    v = b2 * exp_avg_sq.detach().float() + (1.0 - b2) * g * g
+    p = p - lr * weight_decay * p
+    denom = torch.sqrt(v / (1.0 - beta2 ** step)) + eps
+    p = p - (lr / (1.0 - beta1 ** step)) * m / denom
+    return {"param": p.to(param.dtype), "exp_avg": m, "exp_avg_sq": v}
+
+
+# ----------------------------------------------------------------------------------------------
 # vocabulary sharding algebra (what each rank contributes and how the merge must come out)
 # ----------------------------------------------------------------------------------------------
 def shard_stats(hidden: torch.Tensor, weight_shard: torch.Tensor, target: torch.Tensor, vocab_start: int) -> torch.Tensor:
