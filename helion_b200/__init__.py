@@ -8,6 +8,7 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 from .ce_ops import cross_entropy, cross_entropy_backward
 from .install import install, uninstall
 from .matmul_ops import matmul, matmul_vec
+from .norm_ops import residual_rmsnorm, rmsnorm, rmsnorm_backward
 from .optim_ops import adamw_step, clip_grad_norm, grad_sumsq
 from .ops import linear_cross_entropy, linear_cross_entropy_backward
 
@@ -22,5 +23,8 @@ __all__ = [
     "linear_cross_entropy_backward",
     "matmul",
     "matmul_vec",
+    "residual_rmsnorm",
+    "rmsnorm",
+    "rmsnorm_backward",
     "uninstall",
 ]

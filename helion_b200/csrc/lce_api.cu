@@ -13,6 +13,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "ce_kernels.cuh"
+#include "norm_kernels.cuh"
 #include "optim_kernels.cuh"
 #include "row_kernels.cuh"
 
@@ -191,11 +192,11 @@ int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long
     return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
 }
 
-// The same for the CUDA-core GEMM (128 x 32 tiles, up to four CTAs per SM worth of work items).
+// The same for the CUDA-core GEMM (128 x 128 tiles, two CTAs per SM worth of work items).
 int choose_k_splits_simt(long long M, long long Nn, long long K) {
     const long long units = cdiv(M, kBM) * cdiv(Nn, kSimtBN);
-    if (units == 0 || units * 2 > 592) return 1;
-    long long s = 592 / units;
+    if (units == 0 || units * 2 > 296) return 1;
+    long long s = 296 / units;
     if (s > 32) s = 32;
     while (s > 1 && (K / s < 64 || (s - 1) * (cdiv(cdiv(K, s), kSimtBK) * kSimtBK) >= K)) --s;
     return static_cast<int>(s);
@@ -230,7 +231,7 @@ int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool
     const long long m_tiles = cdiv(M, kBM), n_tiles = cdiv(Nn, kSimtBN);
     if (m_tiles * n_tiles > 0x7fffffffll) return LCE_ERR_TOO_LARGE;
     if (m_tiles * n_tiles == 0 || K == 0) return LCE_OK;
-    const long long cap = static_cast<long long>(d.sm_count) * 16;
+    const long long cap = static_cast<long long>(d.sm_count) * 4;
     const long long work = m_tiles * n_tiles * k_splits;
     const int grid = static_cast<int>(work < cap ? work : cap);
     gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(
@@ -1237,6 +1238,327 @@ int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, v
     sumsq_final_kernel<<<1, 1024, 0, s>>>(partials, kSumsqBlocks, out, accumulate);
     LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm / residual RMSNorm
+// ---------------------------------------------------------------------------------------------
+namespace lce {
+namespace {
+
+struct RmsShape {
+    bool wide;    // row does not fit the register-resident kernels
+    bool vector;  // 16-byte accesses are legal
+    int vpt, threads;
+    int rows;     // rows one CTA handles per step (RmsRows<vpt>)
+};
+
+RmsShape rms_shape(long long H, int dtype, bool all_aligned) {
+    const long long vec = 16 / static_cast<long long>(elem_size(dtype));
+    const int max_vpt = RmsTile<float>::kMaxVpt;
+    RmsShape r;
+    r.vector = all_aligned && (H % vec) == 0;
+    const long long nvec = cdiv(H, vec);
+    r.wide = nvec > static_cast<long long>(max_vpt) * kRmsMaxThreads;
+    r.vpt = 1;
+    while (r.vpt < max_vpt && cdiv(nvec, r.vpt) > 256) r.vpt *= 2;
+    const long long threads = cdiv(cdiv(nvec, r.vpt), 32) * 32;
+    r.threads = r.wide ? kRmsMaxThreads : static_cast<int>(threads < 32 ? 32 : threads);
+    r.rows = r.wide ? 1 : (r.vpt >= 4 ? 1 : 4 / r.vpt);
+    return r;
+}
+
+// CTAs for a row kernel of `threads` threads: enough to keep every SM's thread slots full.
+int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) {
+    long long per_sm = 2048 / threads;
+    if (per_sm > 16) per_sm = 16;
+    long long g = static_cast<long long>(d.sm_count) * per_sm;
+    if (cap > 0 && g > cap) g = cap;
+    return static_cast<int>(n_rows < g ? n_rows : g);
+}
+
+// Shared-memory ring of a ring kernel: CTAs per SM by thread count, the per-CTA share of the SM's
+// shared memory, and as many stages (2..4) as fit.
+struct RmsRingPlan {
+    int ctas_per_sm, stages;
+    size_t smem;
+};
+
+RmsRingPlan rms_ring_plan(const RmsShape& sh, long long H, int dtype, int n_streams) {
+    RmsRingPlan p;
+    p.ctas_per_sm = 512 / sh.threads;
+    if (p.ctas_per_sm < 2) p.ctas_per_sm = 2;
+    if (p.ctas_per_sm > 8) p.ctas_per_sm = 8;
+    const size_t stage = static_cast<size_t>(sh.rows) * n_streams * H * elem_size(dtype);
+    const size_t budget = kRmsRingBytesPerSm / p.ctas_per_sm - 2048;  // static shared memory and slack
+    long long st = static_cast<long long>(budget / stage);
+    p.stages = static_cast<int>(st > kRmsMaxStages ? kRmsMaxStages : st);
+    p.smem = p.stages * stage;
+    return p;
+}
+
+// Opt a kernel into more than 48 KB of dynamic shared memory, once per device and kernel.
+template <auto Kernel>
+int rms_ring_opt_in(const DeviceInfo& d) {
+    static std::atomic<bool> done[kMaxDevices];
+    if (!done[d.index].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRmsRingBytesPerSm / 2) !=
+            cudaSuccess)
+            return LCE_ERR_CUDA;
+        done[d.index].store(true, std::memory_order_release);
+    }
+    return LCE_OK;
+}
+
+int rms_ring_grid(const DeviceInfo& d, const RmsShape& sh, const RmsRingPlan& rp, long long n_rows, long long cap) {
+    long long g = static_cast<long long>(d.sm_count) * rp.ctas_per_sm;
+    if (cap > 0 && g > cap) g = cap;
+    const long long groups = cdiv(n_rows, sh.rows);
+    return static_cast<int>(groups < g ? groups : g);
+}
+
+template <class T, bool RESIDUAL>
+int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, const void* residual,
+                       const void* weight, void* out, void* residual_out, float* rstd, long long n_rows,
+                       long long H, float eps, cudaStream_t s) {
+    const T* xp = static_cast<const T*>(x);
+    const T* rp = static_cast<const T*>(residual);
+    const T* rp_src = rp;
+    const T* wp = static_cast<const T*>(weight);
+    T* op = static_cast<T*>(out);
+    T* rop = static_cast<T*>(residual_out);
+    const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
+    if (sh.vector && !sh.wide) {
+        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL ? 2 : 1);
+        if (rp.stages >= 2) {
+            const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);
+            int rc = LCE_OK;
+#define LCE_RMS_RING_FWD(VPT)                                                                                   \
+    rc = rms_ring_opt_in<rms_ring_forward_kernel<T, VPT, RESIDUAL>>(d);                                         \
+    if (rc == LCE_OK)                                                                                            \
+        rms_ring_forward_kernel<T, VPT, RESIDUAL><<<grid, sh.threads, rp.smem, s>>>(xp, rp_, wp, op, rop, rstd, n, h, \
+                                                                                    eps, rp.stages, d.status_ptr)
+            const T* rp_ = rp_src;
+            switch (sh.vpt) {
+                case 1: LCE_RMS_RING_FWD(1); break;
+                case 2: LCE_RMS_RING_FWD(2); break;
+                case 4: LCE_RMS_RING_FWD(4); break;
+                default: LCE_RMS_RING_FWD(8);
+            }
+#undef LCE_RMS_RING_FWD
+            if (rc != LCE_OK) return rc;
+            LCE_COUNT_LAUNCH();
+            return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+        }
+    }
+    const int grid = rms_grid(d, cdiv(n_rows, sh.rows), sh.threads, 0);
+#define LCE_RMS_FWD(VPT, VECTOR) \
+    rms_forward_kernel<T, VPT, VECTOR, RESIDUAL><<<grid, sh.threads, 0, s>>>(xp, rp, wp, op, rop, rstd, n, h, eps)
+    if (sh.wide) {
+        rms_forward_wide_kernel<T, RESIDUAL><<<grid, sh.threads, 0, s>>>(xp, rp, wp, op, rop, rstd, n, h, eps);
+    } else if (sh.vector) {
+        switch (sh.vpt) {
+            case 1: LCE_RMS_FWD(1, true); break;
+            case 2: LCE_RMS_FWD(2, true); break;
+            case 4: LCE_RMS_FWD(4, true); break;
+            default: LCE_RMS_FWD(8, true);
+        }
+    } else {
+        switch (sh.vpt) {
+            case 1: LCE_RMS_FWD(1, false); break;
+            case 2: LCE_RMS_FWD(2, false); break;
+            case 4: LCE_RMS_FWD(4, false); break;
+            default: LCE_RMS_FWD(8, false);
+        }
+    }
+#undef LCE_RMS_FWD
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+// Rows of partial dweight sums the backward writes for (n_rows, H): one per CTA of the row kernel.
+long long rms_partial_rows(long long n_rows, long long H, int dtype) {
+    const RmsShape sh = rms_shape(H, dtype, true);
+    if (sh.wide) {
+        const long long blocks = cdiv(n_rows, 128);
+        return blocks < kRmsMaxPartials ? blocks : kRmsMaxPartials;
+    }
+    return n_rows < kRmsMaxPartials ? n_rows : kRmsMaxPartials;
+}
+
+template <class T>
+int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy, const void* x, const void* weight,
+                        const float* rstd, const void* dres, void* dx, void* dweight, long long n_rows,
+                        long long H, float eps, float* partial, float* rstd_ws, cudaStream_t s) {
+    const T* dyp = static_cast<const T*>(dy);
+    const T* xp = static_cast<const T*>(x);
+    const T* wp = static_cast<const T*>(weight);
+    const T* drp = static_cast<const T*>(dres);
+    T* dxp = static_cast<T*>(dx);
+    const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
+    float* part = dweight != nullptr ? partial : nullptr;
+    int n_partials = 0;
+    if (sh.wide) {
+        const int grid = rms_grid(d, n_rows, sh.threads, 0);
+        float* rs = dweight != nullptr ? rstd_ws : nullptr;
+        rms_backward_wide_kernel<T><<<grid, sh.threads, 0, s>>>(dyp, xp, wp, rstd, drp, dxp, rs, n, h, eps);
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (dweight != nullptr) {
+            n_partials = static_cast<int>(rms_partial_rows(n_rows, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16));
+            const int rows_per_block = static_cast<int>(cdiv(n_rows, n_partials));
+            n_partials = static_cast<int>(cdiv(n_rows, rows_per_block));
+            dim3 g(static_cast<unsigned>(cdiv(H, 256)), static_cast<unsigned>(n_partials));
+            rms_dw_wide_kernel<T><<<g, 256, 0, s>>>(dyp, xp, rs, part, n, h, rows_per_block);
+            LCE_COUNT_LAUNCH();
+            if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        }
+    } else if (sh.vector && rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2).stages >= 2) {
+        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2);
+        const int grid = rms_ring_grid(d, sh, rp, n_rows, kRmsMaxPartials);
+        n_partials = grid;
+        int rc = LCE_OK;
+#define LCE_RMS_RING_BWD(VPT, DRES)                                                                              \
+    rc = rms_ring_opt_in<rms_ring_backward_kernel<T, VPT, DRES>>(d);                                             \
+    if (rc == LCE_OK)                                                                                             \
+        rms_ring_backward_kernel<T, VPT, DRES><<<grid, sh.threads, rp.smem, s>>>(dyp, xp, wp, rstd, drp, dxp, part, n, \
+                                                                                 h, eps, rp.stages, d.status_ptr)
+        if (drp != nullptr) {
+            switch (sh.vpt) {
+                case 1: LCE_RMS_RING_BWD(1, true); break;
+                case 2: LCE_RMS_RING_BWD(2, true); break;
+                case 4: LCE_RMS_RING_BWD(4, true); break;
+                default: LCE_RMS_RING_BWD(8, true);
+            }
+        } else {
+            switch (sh.vpt) {
+                case 1: LCE_RMS_RING_BWD(1, false); break;
+                case 2: LCE_RMS_RING_BWD(2, false); break;
+                case 4: LCE_RMS_RING_BWD(4, false); break;
+                default: LCE_RMS_RING_BWD(8, false);
+            }
+        }
+#undef LCE_RMS_RING_BWD
+        if (rc != LCE_OK) return rc;
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    } else {
+        const int grid = rms_grid(d, cdiv(n_rows, sh.rows), sh.threads, kRmsMaxPartials);
+        n_partials = grid;
+#define LCE_RMS_BWD(VPT, VECTOR) \
+    rms_backward_kernel<T, VPT, VECTOR><<<grid, sh.threads, 0, s>>>(dyp, xp, wp, rstd, drp, dxp, part, n, h, eps)
+        if (sh.vector) {
+            switch (sh.vpt) {
+                case 1: LCE_RMS_BWD(1, true); break;
+                case 2: LCE_RMS_BWD(2, true); break;
+                case 4: LCE_RMS_BWD(4, true); break;
+                default: LCE_RMS_BWD(8, true);
+            }
+        } else {
+            switch (sh.vpt) {
+                case 1: LCE_RMS_BWD(1, false); break;
+                case 2: LCE_RMS_BWD(2, false); break;
+                case 4: LCE_RMS_BWD(4, false); break;
+                default: LCE_RMS_BWD(8, false);
+            }
+        }
+#undef LCE_RMS_BWD
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    if (dweight != nullptr) {
+        dim3 block(32, 8);
+        rms_dw_reduce_kernel<T><<<static_cast<unsigned>(cdiv(H, 32)), block, 0, s>>>(part, n_partials, h,
+                                                                                     static_cast<T*>(dweight));
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    }
+    return LCE_OK;
+}
+
+inline size_t rms_partial_bytes(long long n_rows, long long H, int dtype) {
+    return (static_cast<size_t>(rms_partial_rows(n_rows, H, dtype)) * static_cast<size_t>(H) * sizeof(float) + 255) /
+           256 * 256;
+}
+
+}  // namespace
+}  // namespace lce
+
+extern "C" {
+
+int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
+                        float* rstd, int64_t n_rows, int64_t hidden, float eps, int dtype, void* stream) {
+    using namespace lce;
+    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fffffffll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    if ((residual == nullptr) != (residual_out == nullptr)) return LCE_ERR_ARG;
+    if (n_rows == 0) return LCE_OK;
+    if (!x || !weight || !out) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const bool al = aligned16(x) && aligned16(weight) && aligned16(out) &&
+                    (!residual || (aligned16(residual) && aligned16(residual_out)));
+    const RmsShape sh = rms_shape(hidden, dtype, al);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define LCE_RMS_GO(T)                                                                                              \
+    (residual ? rms_forward_launch<T, true>(*d, sh, x, residual, weight, out, residual_out, rstd, n_rows, hidden, \
+                                            eps, s)                                                                \
+              : rms_forward_launch<T, false>(*d, sh, x, nullptr, weight, out, nullptr, rstd, n_rows, hidden, eps, s))
+    switch (dtype) {
+        case LCE_DTYPE_BF16: return LCE_RMS_GO(__nv_bfloat16);
+        case LCE_DTYPE_F16: return LCE_RMS_GO(__half);
+        default: return LCE_RMS_GO(float);
+    }
+#undef LCE_RMS_GO
+}
+
+size_t lce_rmsnorm_backward_workspace_bytes(int64_t n_rows, int64_t hidden, int dtype) {
+    using namespace lce;
+    if (n_rows <= 0 || hidden < 1) return 0;
+    return rms_partial_bytes(n_rows, hidden, dtype) + (static_cast<size_t>(n_rows) * sizeof(float) + 255) / 256 * 256;
+}
+
+int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, const float* rstd, const void* dresidual,
+                         void* dx, void* dweight, int64_t n_rows, int64_t hidden, float eps, int dtype, void* ws,
+                         size_t ws_bytes, void* stream) {
+    using namespace lce;
+    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fffffffll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n_rows == 0) {  // dweight of an empty batch is zero
+        if (dweight && cudaMemsetAsync(dweight, 0, static_cast<size_t>(hidden) * elem_size(dtype), s) != cudaSuccess)
+            return LCE_ERR_CUDA;
+        return LCE_OK;
+    }
+    if (!dy || !x || !weight || !dx) return LCE_ERR_ARG;
+    float* partial = nullptr;
+    float* rstd_ws = nullptr;
+    if (dweight != nullptr) {
+        if (!ws || ws_bytes < lce_rmsnorm_backward_workspace_bytes(n_rows, hidden, dtype)) return LCE_ERR_WS_TOO_SMALL;
+        if (!aligned16(ws)) return LCE_ERR_ALIGN;
+        partial = static_cast<float*>(ws);
+        rstd_ws = reinterpret_cast<float*>(static_cast<char*>(ws) + rms_partial_bytes(n_rows, hidden, dtype));
+    }
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const bool al = aligned16(dy) && aligned16(x) && aligned16(weight) && aligned16(dx) &&
+                    (!dresidual || aligned16(dresidual));
+    const RmsShape sh = rms_shape(hidden, dtype, al);
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            return rms_backward_launch<__nv_bfloat16>(*d, sh, dy, x, weight, rstd, dresidual, dx, dweight, n_rows, hidden,
+                                                      eps, partial, rstd_ws, s);
+        case LCE_DTYPE_F16:
+            return rms_backward_launch<__half>(*d, sh, dy, x, weight, rstd, dresidual, dx, dweight, n_rows, hidden, eps,
+                                               partial, rstd_ws, s);
+        default:
+            return rms_backward_launch<float>(*d, sh, dy, x, weight, rstd, dresidual, dx, dweight, n_rows, hidden, eps,
+                                              partial, rstd_ws, s);
+    }
 }
 
 }  // extern "C"

@@ -1,0 +1,685 @@
+// RMSNorm and residual-add RMSNorm (the reference's tritium.rmsnorm / residual_rmsnorm /
+// rmsnorm_backward, tritium/ops/rmsnorm.py:29-280): the producer of the hidden states that the
+// fused linear-cross-entropy head consumes. Pure HBM streaming.
+//
+//   forward    z = x (+ residual);  rstd = 1 / sqrt(mean(z^2) + eps);  out = z * rstd * weight
+//   backward   wd = dy * weight;  c = sum(wd * x)
+//              dx = rstd * wd - (rstd^3 / H) * x * c   (+ dresidual)
+//              dweight = sum over rows of dy * x * rstd
+//
+// A CTA keeps one row in registers (VPT 16-byte vectors per thread), so every input element is read
+// from HBM exactly once and every output written once. Unlike the reference, whose backward reads dy
+// and x a second time to form dweight (tritium/ops/rmsnorm.py:383-439), the backward here is a single
+// pass: each thread owns the same columns for every row its CTA walks, accumulates their dweight
+// contributions in registers and writes one partial row per CTA at the end; rms_dw_reduce_kernel adds
+// the partial rows in a fixed order (no atomics: the same bits on every run).
+//
+// Rows too wide for the register-resident form (more than 256 threads x 8 vectors) take the
+// two-pass *_wide kernels; the second pass re-reads the row from L2.
+#pragma once
+
+#include "row_kernels.cuh"
+
+namespace lce {
+
+constexpr int kRmsMaxThreads = 256;
+constexpr int kRmsMaxPartials = 592;  // backward CTAs = partial dweight rows (4 per SM on 148 SMs)
+
+template <class T>
+struct RmsTile {
+    static constexpr int kVec = 16 / sizeof(T);
+    static constexpr int kMaxVpt = 8;  // 256 threads x 8 vectors: 16384 16-bit or 8192 fp32 columns
+};
+
+// Columns c .. c + VEC of one row as a raw 16-byte vector; columns at or beyond H read as zero.
+template <class T, bool VECTOR>
+__device__ __forceinline__ uint4 rms_load(const T* __restrict__ row, int c, int H) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    if (VECTOR) {
+        return c < H ? *reinterpret_cast<const uint4*>(row + c) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        alignas(16) T tmp[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) tmp[j] = (c + j < H) ? row[c + j] : Cvt<T>::from_f(0.f);
+        return *reinterpret_cast<const uint4*>(tmp);
+    }
+}
+
+template <class T>
+__device__ __forceinline__ void rms_unpack(const uint4& raw, float (&v)[RmsTile<T>::kVec]) {
+    alignas(16) T tmp[RmsTile<T>::kVec];
+    *reinterpret_cast<uint4*>(tmp) = raw;
+#pragma unroll
+    for (int j = 0; j < RmsTile<T>::kVec; ++j) v[j] = Cvt<T>::to_f(tmp[j]);
+}
+
+template <class T>
+__device__ __forceinline__ uint4 rms_pack(const float (&v)[RmsTile<T>::kVec]) {
+    alignas(16) T tmp[RmsTile<T>::kVec];
+#pragma unroll
+    for (int j = 0; j < RmsTile<T>::kVec; ++j) tmp[j] = Cvt<T>::from_f(v[j]);
+    return *reinterpret_cast<const uint4*>(tmp);
+}
+
+template <class T, bool VECTOR>
+__device__ __forceinline__ void rms_store(T* __restrict__ row, int c, int H, const uint4& raw) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    if (VECTOR) {
+        if (c < H) *reinterpret_cast<uint4*>(row + c) = raw;
+    } else {
+        alignas(16) T tmp[VEC];
+        *reinterpret_cast<uint4*>(tmp) = raw;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j)
+            if (c + j < H) row[c + j] = tmp[j];
+    }
+}
+
+// Sums NV values over the CTA; every thread gets the totals. Warp shuffles, then the warp totals in
+// warp order - a fixed order, so the result does not depend on timing. `red` holds NV x 32 floats and
+// must not be reused before the next __syncthreads() (callers alternate two buffers).
+template <int NV>
+__device__ __forceinline__ void rms_block_sum(float (&v)[NV], float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
+        if (lane == 0) red[i * 32 + warp] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        float s = 0.f;
+        for (int w = 0; w < n_warps; ++w) s += red[i * 32 + w];
+        v[i] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward (register-resident rows)
+// A CTA walks groups of ROWS consecutive rows: the loads of all ROWS rows are issued before anything
+// is reduced (ROWS x VPT 16-byte vectors in flight per thread and input - what keeps HBM busy when a
+// row is only a few KB), and the ROWS row sums share one barrier. The rows stay PACKED in registers
+// across the barrier and are unpacked again for the output pass.
+// ---------------------------------------------------------------------------------------------
+template <int VPT>
+struct RmsRows {
+    static constexpr int kRows = VPT >= 4 ? 1 : 4 / VPT;  // ROWS x VPT >= 4 vectors per thread and input
+};
+
+template <class T, int VPT, bool VECTOR, bool RESIDUAL>
+__global__ void __launch_bounds__(kRmsMaxThreads)
+rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
+                   T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
+                   int n_rows, int H, float eps) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    constexpr int ROWS = RmsRows<VPT>::kRows;
+    __shared__ float red[2][ROWS * 32];
+    const int t = threadIdx.x;
+
+    uint4 wraw[VPT];  // this thread's weight columns, loaded once
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) wraw[i] = rms_load<T, VECTOR>(weight, (i * blockDim.x + t) * VEC, H);
+
+    int it = 0;
+    for (int row0 = blockIdx.x * ROWS; row0 < n_rows; row0 += gridDim.x * ROWS, ++it) {
+        uint4 rx[ROWS][VPT], rr[RESIDUAL ? ROWS : 1][VPT];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const long long off = static_cast<long long>(row0 + r) * H;
+            const int h = row0 + r < n_rows ? H : 0;  // rows past the end read as zeros
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int c = (i * blockDim.x + t) * VEC;
+                rx[r][i] = rms_load<T, VECTOR>(x + off, c, h);
+                if (RESIDUAL) rr[r][i] = rms_load<T, VECTOR>(residual + off, c, h);
+            }
+        }
+        float ss[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const long long off = static_cast<long long>(row0 + r) * H;
+            const int h = row0 + r < n_rows ? H : 0;
+            ss[r] = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                float z[VEC];
+                rms_unpack<T>(rx[r][i], z);
+                if (RESIDUAL) {
+                    float q[VEC];
+                    rms_unpack<T>(rr[r][i], q);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) z[j] += q[j];
+                    rms_store<T, VECTOR>(residual_out + off, (i * blockDim.x + t) * VEC, h, rms_pack<T>(z));
+                }
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) ss[r] = fmaf(z[j], z[j], ss[r]);
+            }
+        }
+        rms_block_sum<ROWS>(ss, red[it & 1]);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const long long off = static_cast<long long>(row0 + r) * H;
+            const int h = row0 + r < n_rows ? H : 0;
+            const float rstd = 1.0f / sqrtf(ss[r] / static_cast<float>(H) + eps);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                float z[VEC], w[VEC];
+                rms_unpack<T>(rx[r][i], z);
+                if (RESIDUAL) {
+                    float q[VEC];
+                    rms_unpack<T>(rr[r][i], q);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) z[j] += q[j];
+                }
+                rms_unpack<T>(wraw[i], w);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * w[j];
+                rms_store<T, VECTOR>(out + off, (i * blockDim.x + t) * VEC, h, rms_pack<T>(z));
+            }
+            if (t == 0 && rstd_out != nullptr && h != 0) rstd_out[row0 + r] = rstd;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Ring kernels: the form every 16-byte-aligned problem takes.
+//
+// A row is only a few KB, so what keeps HBM busy is how many bytes a CTA has in flight - and registers
+// are a poor landing zone for them. Here one elected thread streams groups of ROWS consecutive rows
+// (contiguous in memory: one bulk copy per input tensor) into a ring of shared-memory stages with
+// cp.async.bulk, completion counted on an mbarrier per stage; the CTA's threads compute out of shared
+// memory (each thread owns the same columns of every row, two passes over the stage: row sums, then
+// outputs) and write results straight to global memory. The stage is refilled as soon as the CTA is
+// done with it, so up to STAGES - 1 stages per CTA are always in flight regardless of register use.
+// Waits on the mbarriers are bounded; on a timeout the CTA records kDevErrNormTimeout in the device
+// status word, drains what it issued (bounded again) and returns.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRmsMaxStages = 4;
+constexpr int kRmsRingBytesPerSm = 200 * 1024;
+constexpr int kDevErrNormTimeout = 111;
+
+struct RmsRing {
+    uint64_t full[kRmsMaxStages];
+    int abort_flag;
+    int drain_flag;
+};
+
+// Thread 0: start the loads of this CTA's k-th row group into stage k % stages (nothing if the group
+// does not exist). `src` holds NS input tensors; stage layout = [tensor][row in group][H].
+template <class T, int ROWS, int NS>
+__device__ __forceinline__ void rms_ring_issue(RmsRing& ring, unsigned char* data, const T* const* src, int k,
+                                               int stages, int n_rows, int H) {
+    const long long group = blockIdx.x + static_cast<long long>(k) * gridDim.x;
+    const long long row0 = group * ROWS;
+    if (row0 >= n_rows) return;
+    const int s = k % stages;
+    const int nr = n_rows - row0 < ROWS ? static_cast<int>(n_rows - row0) : ROWS;
+    const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+    const uint32_t bar = ptx::smem_u32(&ring.full[s]);
+    ptx::mbar_arrive_expect_tx(bar, nr * row_bytes * NS);
+    unsigned char* dst = data + static_cast<size_t>(s) * (ROWS * NS * row_bytes);
+#pragma unroll
+    for (int n = 0; n < NS; ++n)
+        ptx::bulk_load_1d(ptx::smem_u32(dst + n * ROWS * row_bytes), src[n] + row0 * H, nr * row_bytes, bar);
+}
+
+// After a timeout: thread 0 waits (bounded) for the loads that were issued but never consumed, so that
+// no copy is still writing into this CTA's shared memory when it exits.
+__device__ __forceinline__ void rms_ring_drain(RmsRing& ring, int k_next, int stages, long long n_groups, int* status) {
+    atomicCAS(status, 0, kDevErrNormTimeout);
+    ring.drain_flag = 0;
+    for (int k = k_next; k < k_next + stages; ++k) {
+        if (blockIdx.x + static_cast<long long>(k) * gridDim.x >= n_groups) break;
+        ptx::mbar_wait(ptx::smem_u32(&ring.full[k % stages]), (k / stages) & 1, &ring.drain_flag);
+    }
+}
+
+template <class T, int VPT, bool RESIDUAL>
+__global__ void __launch_bounds__(kRmsMaxThreads, 2)
+rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
+                        T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
+                        int n_rows, int H, float eps, int stages, int* __restrict__ status) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    constexpr int ROWS = RmsRows<VPT>::kRows;
+    constexpr int NS = RESIDUAL ? 2 : 1;
+    extern __shared__ __align__(128) unsigned char ring_data[];
+    __shared__ RmsRing ring;
+    __shared__ float red[2][ROWS * 32];
+    const int t = threadIdx.x;
+    const long long n_groups = (static_cast<long long>(n_rows) + ROWS - 1) / ROWS;
+    const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+    const T* const srcs[2] = {x, residual};
+
+    if (t == 0) {
+        for (int s = 0; s < stages; ++s) ptx::mbar_init(ptx::smem_u32(&ring.full[s]), 1);
+        ring.abort_flag = 0;
+        ptx::fence_mbar_init();
+        for (int k = 0; k < stages; ++k) rms_ring_issue<T, ROWS, NS>(ring, ring_data, srcs, k, stages, n_rows, H);
+    }
+    uint4 wraw[VPT];  // this thread's weight columns
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) wraw[i] = rms_load<T, true>(weight, (i * blockDim.x + t) * VEC, H);
+    __syncthreads();
+
+    int k = 0;
+    bool failed = false;
+    for (;; ++k) {
+        const long long group = blockIdx.x + static_cast<long long>(k) * gridDim.x;
+        if (group >= n_groups) break;
+        const long long row0 = group * ROWS;
+        const int s = k % stages;
+        ptx::mbar_wait(ptx::smem_u32(&ring.full[s]), (k / stages) & 1, &ring.abort_flag);
+        const unsigned char* st = ring_data + static_cast<size_t>(s) * (ROWS * NS * row_bytes);
+        float ss[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            ss[r] = 0.f;
+            if (row0 + r < n_rows) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int c = (i * blockDim.x + t) * VEC;
+                    if (c < H) {
+                        float z[VEC];
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), z);
+                        if (RESIDUAL) {
+                            float q[VEC];
+                            rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), q);
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) z[j] += q[j];
+                            *reinterpret_cast<uint4*>(residual_out + (row0 + r) * H + c) = rms_pack<T>(z);
+                        }
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) ss[r] = fmaf(z[j], z[j], ss[r]);
+                    }
+                }
+            }
+        }
+        rms_block_sum<ROWS>(ss, red[k & 1]);
+        if (ring.abort_flag) {  // written before the barrier inside rms_block_sum: every thread sees it
+            failed = true;
+            break;
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (row0 + r < n_rows) {
+                const float rstd = 1.0f / sqrtf(ss[r] / static_cast<float>(H) + eps);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int c = (i * blockDim.x + t) * VEC;
+                    if (c < H) {
+                        float z[VEC], w[VEC];
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), z);
+                        if (RESIDUAL) {
+                            float q[VEC];
+                            rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), q);
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) z[j] += q[j];
+                        }
+                        rms_unpack<T>(wraw[i], w);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * w[j];
+                        *reinterpret_cast<uint4*>(out + (row0 + r) * H + c) = rms_pack<T>(z);
+                    }
+                }
+                if (t == 0 && rstd_out != nullptr) rstd_out[row0 + r] = rstd;
+            }
+        }
+        __syncthreads();  // the CTA is done with stage s
+        if (t == 0) {
+            ptx::fence_proxy_async_smem();
+            rms_ring_issue<T, ROWS, NS>(ring, ring_data, srcs, k + stages, stages, n_rows, H);
+        }
+    }
+    if (failed && t == 0) rms_ring_drain(ring, k, stages, n_groups, status);
+}
+
+// Backward on the ring. NS = 2 (dy, x) or 3 (+ dresidual). The dweight contributions of the columns a
+// thread owns stay in its registers over all the rows its CTA walks; partial[blockIdx.x][H] at the end.
+template <class T, int VPT, bool DRES>
+__global__ void __launch_bounds__(kRmsMaxThreads, 2)
+rms_ring_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ weight,
+                         const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
+                         float* __restrict__ partial, int n_rows, int H, float eps, int stages,
+                         int* __restrict__ status) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    constexpr int ROWS = RmsRows<VPT>::kRows;
+    constexpr int NS = DRES ? 3 : 2;
+    constexpr bool kWeightInRegs = VPT * VEC <= 16;
+    extern __shared__ __align__(128) unsigned char ring_data[];
+    __shared__ RmsRing ring;
+    __shared__ float red[2][2 * ROWS * 32];
+    const int t = threadIdx.x;
+    const long long n_groups = (static_cast<long long>(n_rows) + ROWS - 1) / ROWS;
+    const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+    const T* const srcs[3] = {dy, x, dres};
+
+    if (t == 0) {
+        for (int s = 0; s < stages; ++s) ptx::mbar_init(ptx::smem_u32(&ring.full[s]), 1);
+        ring.abort_flag = 0;
+        ptx::fence_mbar_init();
+        for (int k = 0; k < stages; ++k) rms_ring_issue<T, ROWS, NS>(ring, ring_data, srcs, k, stages, n_rows, H);
+    }
+    uint4 wraw[kWeightInRegs ? VPT : 1];
+    if (kWeightInRegs) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) wraw[i] = rms_load<T, true>(weight, (i * blockDim.x + t) * VEC, H);
+    }
+    float dwacc[VPT][VEC];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) dwacc[i][j] = 0.f;
+    __syncthreads();
+
+    int k = 0;
+    bool failed = false;
+    for (;; ++k) {
+        const long long group = blockIdx.x + static_cast<long long>(k) * gridDim.x;
+        if (group >= n_groups) break;
+        const long long row0 = group * ROWS;
+        const int s = k % stages;
+        ptx::mbar_wait(ptx::smem_u32(&ring.full[s]), (k / stages) & 1, &ring.abort_flag);
+        const unsigned char* st = ring_data + static_cast<size_t>(s) * (ROWS * NS * row_bytes);
+        // pass A: per row c = sum(dy * w * x) and sum(x^2)
+        float sums[2 * ROWS];
+#pragma unroll
+        for (int r = 0; r < 2 * ROWS; ++r) sums[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = (i * blockDim.x + t) * VEC;
+            if (c < H) {
+                float w[VEC];
+                if (kWeightInRegs) rms_unpack<T>(wraw[i], w);
+                else rms_unpack<T>(*reinterpret_cast<const uint4*>(weight + c), w);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    if (row0 + r < n_rows) {
+                        float d[VEC], xv[VEC];
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), d);
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), xv);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) {
+                            sums[2 * r] = fmaf(d[j] * w[j], xv[j], sums[2 * r]);
+                            sums[2 * r + 1] = fmaf(xv[j], xv[j], sums[2 * r + 1]);
+                        }
+                    }
+                }
+            }
+        }
+        rms_block_sum<2 * ROWS>(sums, red[k & 1]);
+        if (ring.abort_flag) {
+            failed = true;
+            break;
+        }
+        // pass B: dx and the dweight contributions
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (row0 + r < n_rows) {
+                const float rstd = rstd_in != nullptr ? rstd_in[row0 + r]
+                                                      : 1.0f / sqrtf(sums[2 * r + 1] / static_cast<float>(H) + eps);
+                const float coef = rstd * rstd * rstd / static_cast<float>(H);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int c = (i * blockDim.x + t) * VEC;
+                    if (c < H) {
+                        float w[VEC], d[VEC], xv[VEC], o[VEC];
+                        if (kWeightInRegs) rms_unpack<T>(wraw[i], w);
+                        else rms_unpack<T>(*reinterpret_cast<const uint4*>(weight + c), w);
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), d);
+                        rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), xv);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) {
+                            dwacc[i][j] = fmaf(d[j] * xv[j], rstd, dwacc[i][j]);
+                            o[j] = rstd * (d[j] * w[j]) - coef * xv[j] * sums[2 * r];
+                        }
+                        if (DRES) {
+                            float q[VEC];
+                            rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (2 * ROWS + r) * row_bytes + c * sizeof(T)), q);
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) o[j] = Cvt<T>::to_f(Cvt<T>::from_f(o[j])) + q[j];
+                        }
+                        *reinterpret_cast<uint4*>(dx + (row0 + r) * H + c) = rms_pack<T>(o);
+                    }
+                }
+            }
+        }
+        __syncthreads();  // the CTA is done with stage s
+        if (t == 0) {
+            ptx::fence_proxy_async_smem();
+            rms_ring_issue<T, ROWS, NS>(ring, ring_data, srcs, k + stages, stages, n_rows, H);
+        }
+    }
+    if (failed && t == 0) rms_ring_drain(ring, k, stages, n_groups, status);
+    if (partial != nullptr) {
+        float* prow = partial + static_cast<long long>(blockIdx.x) * H;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = (i * blockDim.x + t) * VEC;
+            if (c < H) {
+                float4* dst = reinterpret_cast<float4*>(prow + c);
+#pragma unroll
+                for (int j = 0; j < VEC; j += 4)
+                    dst[j / 4] = make_float4(dwacc[i][j], dwacc[i][j + 1], dwacc[i][j + 2], dwacc[i][j + 3]);
+            }
+        }
+    }
+}
+
+// forward, any width: two passes over the row (the second one hits L2)
+template <class T, bool RESIDUAL>
+__global__ void __launch_bounds__(kRmsMaxThreads)
+rms_forward_wide_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
+                        T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
+                        int n_rows, int H, float eps) {
+    __shared__ float red[2][32];
+    int it = 0;
+    for (int row = blockIdx.x; row < n_rows; row += gridDim.x, ++it) {
+        const long long off = static_cast<long long>(row) * H;
+        float ss[1] = {0.f};
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float z = Cvt<T>::to_f(x[off + c]);
+            if (RESIDUAL) {
+                z += Cvt<T>::to_f(residual[off + c]);
+                residual_out[off + c] = Cvt<T>::from_f(z);
+            }
+            ss[0] = fmaf(z, z, ss[0]);
+        }
+        rms_block_sum<1>(ss, red[it & 1]);
+        const float rstd = 1.0f / sqrtf(ss[0] / static_cast<float>(H) + eps);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float z = Cvt<T>::to_f(x[off + c]);
+            if (RESIDUAL) z += Cvt<T>::to_f(residual[off + c]);
+            out[off + c] = Cvt<T>::from_f(z * rstd * Cvt<T>::to_f(weight[c]));
+        }
+        if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward (register-resident row, dweight partials in registers)
+//   rstd_in == nullptr  recompute rstd from x and eps (the reference's rmsnorm_backward)
+//   dres != nullptr     dx = round(dx) + dres, the two roundings of the reference's
+//                       `dz.add_(dresidual_out)` on a tensor of the input dtype
+//   partial != nullptr  this CTA's dweight contributions go to partial[blockIdx.x][H]
+// ---------------------------------------------------------------------------------------------
+template <class T, int VPT, bool VECTOR>
+__global__ void __launch_bounds__(kRmsMaxThreads)
+rms_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ weight,
+                    const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
+                    float* __restrict__ partial, int n_rows, int H, float eps) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    constexpr int ROWS = RmsRows<VPT>::kRows;
+    constexpr bool kWeightInRegs = VPT * VEC <= 16;  // wider rows re-read the weights (L1 hits) every step
+    __shared__ float red[2][2 * ROWS * 32];
+    const int t = threadIdx.x;
+
+    uint4 wraw[kWeightInRegs ? VPT : 1];
+    if (kWeightInRegs) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) wraw[i] = rms_load<T, VECTOR>(weight, (i * blockDim.x + t) * VEC, H);
+    }
+    float dwacc[VPT][VEC];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) dwacc[i][j] = 0.f;
+
+    int it = 0;
+    for (int row0 = blockIdx.x * ROWS; row0 < n_rows; row0 += gridDim.x * ROWS, ++it) {
+        uint4 rdy[ROWS][VPT], rx[ROWS][VPT];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const long long off = static_cast<long long>(row0 + r) * H;
+            const int h = row0 + r < n_rows ? H : 0;  // rows past the end read as zeros
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int c = (i * blockDim.x + t) * VEC;
+                rdy[r][i] = rms_load<T, VECTOR>(dy + off, c, h);
+                rx[r][i] = rms_load<T, VECTOR>(x + off, c, h);
+            }
+        }
+        // pass A over the registers: per row c = sum(dy * w * x) and sum(x^2)
+        float sums[2 * ROWS];
+#pragma unroll
+        for (int r = 0; r < 2 * ROWS; ++r) sums[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float w[VEC];
+            if (kWeightInRegs) rms_unpack<T>(wraw[i], w);
+            else rms_unpack<T>(rms_load<T, VECTOR>(weight, (i * blockDim.x + t) * VEC, H), w);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                float d[VEC], xv[VEC];
+                rms_unpack<T>(rdy[r][i], d);
+                rms_unpack<T>(rx[r][i], xv);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    sums[2 * r] = fmaf(d[j] * w[j], xv[j], sums[2 * r]);
+                    sums[2 * r + 1] = fmaf(xv[j], xv[j], sums[2 * r + 1]);
+                }
+            }
+        }
+        rms_block_sum<2 * ROWS>(sums, red[it & 1]);
+        // pass B: the rows stayed packed in registers; unpack one vector at a time
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const long long off = static_cast<long long>(row0 + r) * H;
+            const int h = row0 + r < n_rows ? H : 0;
+            float rstd = 0.f;  // a row past the end adds nothing to dweight
+            if (h != 0)
+                rstd = rstd_in != nullptr ? rstd_in[row0 + r]
+                                          : 1.0f / sqrtf(sums[2 * r + 1] / static_cast<float>(H) + eps);
+            const float coef = rstd * rstd * rstd / static_cast<float>(H);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int c = (i * blockDim.x + t) * VEC;
+                float w[VEC], d[VEC], xv[VEC], o[VEC];
+                if (kWeightInRegs) rms_unpack<T>(wraw[i], w);
+                else rms_unpack<T>(rms_load<T, VECTOR>(weight, c, H), w);
+                rms_unpack<T>(rdy[r][i], d);
+                rms_unpack<T>(rx[r][i], xv);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    dwacc[i][j] = fmaf(d[j] * xv[j], rstd, dwacc[i][j]);
+                    o[j] = rstd * (d[j] * w[j]) - coef * xv[j] * sums[2 * r];
+                }
+                if (dres != nullptr) {
+                    float q[VEC];
+                    rms_unpack<T>(rms_load<T, VECTOR>(dres + off, c, h), q);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) o[j] = Cvt<T>::to_f(Cvt<T>::from_f(o[j])) + q[j];
+                }
+                rms_store<T, VECTOR>(dx + off, c, h, rms_pack<T>(o));
+            }
+        }
+    }
+    if (partial != nullptr) {
+        float* prow = partial + static_cast<long long>(blockIdx.x) * H;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = (i * blockDim.x + t) * VEC;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                if (c + j < H) prow[c + j] = dwacc[i][j];
+        }
+    }
+}
+
+// backward, any width: pass 1 forms c (and rstd), pass 2 writes dx; rstd goes to rstd_ws for the
+// column kernel below.
+template <class T>
+__global__ void __launch_bounds__(kRmsMaxThreads)
+rms_backward_wide_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ weight,
+                         const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
+                         float* __restrict__ rstd_ws, int n_rows, int H, float eps) {
+    __shared__ float red[2][64];
+    int it = 0;
+    for (int row = blockIdx.x; row < n_rows; row += gridDim.x, ++it) {
+        const long long off = static_cast<long long>(row) * H;
+        float sums[2] = {0.f, 0.f};
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float xv = Cvt<T>::to_f(x[off + c]);
+            const float wd = Cvt<T>::to_f(dy[off + c]) * Cvt<T>::to_f(weight[c]);
+            sums[0] = fmaf(wd, xv, sums[0]);
+            sums[1] = fmaf(xv, xv, sums[1]);
+        }
+        rms_block_sum<2>(sums, red[it & 1]);
+        const float rstd = rstd_in != nullptr ? rstd_in[row] : 1.0f / sqrtf(sums[1] / static_cast<float>(H) + eps);
+        const float coef = rstd * rstd * rstd / static_cast<float>(H);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float xv = Cvt<T>::to_f(x[off + c]);
+            const float wd = Cvt<T>::to_f(dy[off + c]) * Cvt<T>::to_f(weight[c]);
+            float o = rstd * wd - coef * xv * sums[0];
+            if (dres != nullptr) o = Cvt<T>::to_f(Cvt<T>::from_f(o)) + Cvt<T>::to_f(dres[off + c]);
+            dx[off + c] = Cvt<T>::from_f(o);
+        }
+        if (threadIdx.x == 0 && rstd_ws != nullptr) rstd_ws[row] = rstd;
+    }
+}
+
+// dweight partials for the wide form: one thread per column, one partial row per block of rows.
+template <class T>
+__global__ void __launch_bounds__(256)
+rms_dw_wide_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ rstd,
+                   float* __restrict__ partial, int n_rows, int H, int rows_per_block) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= H) return;
+    const int r0 = blockIdx.y * rows_per_block;
+    const int r1 = min(n_rows, r0 + rows_per_block);
+    float acc = 0.f;
+    for (int r = r0; r < r1; ++r) {
+        const long long off = static_cast<long long>(r) * H + col;
+        acc = fmaf(Cvt<T>::to_f(dy[off]) * Cvt<T>::to_f(x[off]), rstd[r], acc);
+    }
+    partial[static_cast<long long>(blockIdx.y) * H + col] = acc;
+}
+
+// dweight[col] = sum over partial rows, in a fixed order: 8 strided sub-sums per column, then those
+// 8 in order. Block (32, 8): 32 consecutive columns per CTA.
+template <class T>
+__global__ void __launch_bounds__(256)
+rms_dw_reduce_kernel(const float* __restrict__ partial, int n_partials, int H, T* __restrict__ dweight) {
+    __shared__ float sm[8][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    float a0 = 0.f, a1 = 0.f;
+    if (col < H) {
+        int p = threadIdx.y;
+        for (; p + 8 < n_partials; p += 16) {
+            a0 += partial[static_cast<long long>(p) * H + col];
+            a1 += partial[static_cast<long long>(p + 8) * H + col];
+        }
+        if (p < n_partials) a0 += partial[static_cast<long long>(p) * H + col];
+    }
+    sm[threadIdx.y][threadIdx.x] = a0 + a1;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < H) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += sm[k][threadIdx.x];
+        dweight[col] = Cvt<T>::from_f(s);
+    }
+}
+
+}  // namespace lce

@@ -13,14 +13,17 @@ import importlib
 import sys
 from types import ModuleType
 
-from . import ce_ops, matmul_ops, ops, optim_ops
+from . import ce_ops, matmul_ops, norm_ops, ops, optim_ops
 
 # the fused op (the path this package exists for), the plain op of the same reference file, and the
 # matrix product that runs on the same GEMM cores
 NAMES = ("linear_cross_entropy", "linear_cross_entropy_backward", "cross_entropy", "cross_entropy_backward",
-         "matmul", "matmul_vec", "adamw_step")
+         "matmul", "matmul_vec", "adamw_step", "rmsnorm", "residual_rmsnorm", "rmsnorm_backward")
 _IMPL = {
     "adamw_step": optim_ops.adamw_step,
+    "rmsnorm": norm_ops.rmsnorm,
+    "residual_rmsnorm": norm_ops.residual_rmsnorm,
+    "rmsnorm_backward": norm_ops.rmsnorm_backward,
     "matmul": matmul_ops.matmul,
     "matmul_vec": matmul_ops.matmul_vec,
     "linear_cross_entropy": ops.linear_cross_entropy,
@@ -28,7 +31,8 @@ _IMPL = {
     "cross_entropy": ce_ops.cross_entropy,
     "cross_entropy_backward": ce_ops.cross_entropy_backward,
 }
-MODULES = ("tritium", "tritium.ops", "tritium.ops.cross_entropy", "tritium.ops.matmul", "tritium.ops.adamw")
+MODULES = ("tritium", "tritium.ops", "tritium.ops.cross_entropy", "tritium.ops.matmul", "tritium.ops.adamw",
+           "tritium.ops.rmsnorm")
 
 _saved: dict[tuple[str, str], object] = {}
 
@@ -38,7 +42,8 @@ def _targets(root: ModuleType | None) -> list[ModuleType]:
     # (tritium/ops/__init__.py), so the submodules are taken from the import system, not via getattr.
     base = MODULES[0] if root is None else root.__name__
     mods = [importlib.import_module(base) if root is None else root]
-    for suffix in (".ops", ".ops.cross_entropy", ".ops.matmul", ".ops.adamw"):
+    # (the same holds for `tritium.ops.matmul` and `tritium.ops.rmsnorm`)
+    for suffix in (".ops", ".ops.cross_entropy", ".ops.matmul", ".ops.adamw", ".ops.rmsnorm"):
         name = base + suffix
         mod = sys.modules.get(name)
         if mod is None:

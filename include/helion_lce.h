@@ -222,6 +222,27 @@ size_t lce_sumsq_workspace_bytes(void);
 int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, void* ws, size_t ws_bytes,
               void* stream);
 
+/* ---- producer of the hidden states -----------------------------------------------------------------
+ * lce_rmsnorm_forward replaces the launches of tritium.rmsnorm and tritium.residual_rmsnorm
+ * (tritium/ops/rmsnorm.py:29-84, :325-349, :749-778) on [n_rows, hidden] row-major tensors of `dtype`:
+ *   z = x (+ residual);  rstd = 1 / sqrt(mean(z^2) + eps);  out = z * rstd * weight     (fp32 arithmetic)
+ * residual, residual_out: both NULL (plain rmsnorm) or both set (residual_out = z rounded to dtype).
+ * rstd: NULL or [n_rows] float32 (what the reference saves for backward).
+ * lce_rmsnorm_backward replaces tritium.rmsnorm_backward and the backward of both autograd functions
+ * (tritium/ops/rmsnorm.py:105-280, :383-616, :697-734):
+ *   dx = rstd * dy * weight - (rstd^3 / hidden) * x * sum(dy * weight * x)   (+ dresidual, when not NULL)
+ *   dweight = sum over rows of dy * x * rstd      (NULL: not computed)
+ * x is the normalised tensor (residual_out for the residual form). rstd NULL: recomputed from x and eps.
+ * One pass over dy and x; dweight is summed in a fixed order (identical bits from run to run, where the
+ * reference uses atomics below hidden = 512). ws: lce_rmsnorm_backward_workspace_bytes(), needed only
+ * when dweight is wanted. hidden is limited by memory only (the reference stops at 65536). */
+int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
+                        float* rstd, int64_t n_rows, int64_t hidden, float eps, int dtype, void* stream);
+size_t lce_rmsnorm_backward_workspace_bytes(int64_t n_rows, int64_t hidden, int dtype);
+int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, const float* rstd,
+                         const void* dresidual, void* dx, void* dweight, int64_t n_rows, int64_t hidden, float eps,
+                         int dtype, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- test hook -------------------------------------------------------------------------------
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
  * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b

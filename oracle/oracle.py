@@ -249,6 +249,70 @@ def restated_adamw_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.
 
 
 # ----------------------------------------------------------------------------------------------
+# producer of the hidden states: RMSNorm / residual RMSNorm
+# ----------------------------------------------------------------------------------------------
+def restated_rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                             residual: torch.Tensor | None = None) -> dict:
+    """The reference's forward kernels (tritium/ops/rmsnorm.py:29-84) in fp32 torch: the sum is
+    formed in fp32 (float64 here, rounded once, so the restatement does not depend on a summation
+    order), the outputs are rounded to the input dtype. With ``residual`` the normalised value is
+    the UNROUNDED fp32 sum z = x + residual (:76-81); ``residual_out`` is z rounded."""
+    z = x.detach().float()
+    if residual is not None:
+        z = z + residual.detach().float()
+    mean_sq = (z.double() * z.double()).mean(dim=-1, keepdim=True).float()
+    rstd = 1.0 / torch.sqrt(mean_sq + torch.tensor(eps, dtype=torch.float32))
+    out = (z * rstd * weight.detach().float()).to(x.dtype)
+    res = {"out": out, "rstd": rstd.reshape(-1)}
+    if residual is not None:
+        res["residual_out"] = z.to(x.dtype)
+    return res
+
+
+def restated_rmsnorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                              rstd: torch.Tensor | None = None, dresidual: torch.Tensor | None = None) -> dict:
+    """The reference's backward (tritium/ops/rmsnorm.py:105-130, :225-280): dx per row from the saved
+    (or recomputed, :163-191) rstd, dweight = sum over rows of dy * x * rstd in fp32, both rounded to
+    the input dtype. ``dresidual`` is added the way the residual autograd function adds it (:728):
+    onto the already rounded dx, in the input dtype."""
+    h = x.shape[-1]
+    xf = x.detach().float().reshape(-1, h)
+    dyf = dy.detach().float().reshape(-1, h)
+    wf = weight.detach().float()
+    if rstd is None:
+        mean_sq = (xf.double() * xf.double()).mean(dim=-1, keepdim=True).float()
+        r = 1.0 / torch.sqrt(mean_sq + torch.tensor(eps, dtype=torch.float32))
+    else:
+        r = rstd.detach().float().reshape(-1, 1)
+    weighted = dyf * wf
+    c = (weighted.double() * xf.double()).sum(dim=-1, keepdim=True).float()
+    dx = (r * weighted - (r * r * r / h) * xf * c).to(x.dtype)
+    if dresidual is not None:
+        dx = dx + dresidual.detach().reshape(-1, h).to(x.dtype)
+    dweight = (dyf.double() * xf.double() * r.double()).sum(dim=0).float().to(weight.dtype)
+    return {"dx": dx.reshape(x.shape), "dweight": dweight}
+
+
+def rmsnorm_expression(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                       residual: torch.Tensor | None = None, *, dy: torch.Tensor | None = None,
+                       dresidual_out: torch.Tensor | None = None) -> dict:
+    """What the op MEANS, through torch autograd in float64: out = z * rsqrt(mean(z^2) + eps) * w with
+    z = x (+ residual), and the gradients of sum(out * dy) (+ sum(z * dresidual_out))."""
+    xd = x.detach().double().requires_grad_(dy is not None)
+    wd = weight.detach().double().requires_grad_(dy is not None)
+    z = xd if residual is None else xd + residual.detach().double()
+    out = z * torch.rsqrt((z * z).mean(dim=-1, keepdim=True) + eps) * wd
+    res = {"out": out.detach(), "z": z.detach()}
+    if dy is not None:
+        obj = (out * dy.detach().double()).sum()
+        if dresidual_out is not None:
+            obj = obj + (z * dresidual_out.detach().double()).sum()
+        obj.backward()
+        res["dx"], res["dweight"] = xd.grad, wd.grad
+    return res
+
+
+# ----------------------------------------------------------------------------------------------
 # vocabulary sharding algebra (what each rank contributes and how the merge must come out)
 # ----------------------------------------------------------------------------------------------
 def shard_stats(hidden: torch.Tensor, weight_shard: torch.Tensor, target: torch.Tensor, vocab_start: int) -> torch.Tensor:

@@ -13,6 +13,11 @@
         (torch 2.11.0+cu128, triton 3.6.0). It pins the oracle's restatement of the reference
         algorithm and is the closest thing to a golden vector the path has: the reference ships none.
 
+    python tests/golden/make_golden.py --reference-rmsnorm OUT.pt
+        The same for the producer of the hidden states: tritium.rmsnorm, tritium.residual_rmsnorm (forward,
+        autograd backward) and tritium.rmsnorm_backward on the cases of rmsnorm_case_list(). The committed
+        reference_b200_rmsnorm.pt came from this mode on a B200.
+
 Cases follow the reference's own tests (tests/tritium/test_cross_entropy.py:59-109: H=64, V in
 {128, 1024}, N in {1, 16, 128}, std-1 weights; autograd at N=32, H=64, V=256; 3-D hidden) plus one
 shape that takes the reference's large-shape backward branch (row-chunk loop over cuBLAS GEMMs).
@@ -73,6 +78,72 @@ def make_case_inputs(case: dict, index: int) -> dict:
     target = torch.randint(0, case["v"], case["shape"], generator=g)
     return {"hidden": hidden, "weight": weight, "target": target,
             "grad_out": torch.tensor(case.get("grad_out", 1.0), dtype=torch.float32)}
+
+
+def rmsnorm_case_list() -> list[dict]:
+    """Shapes after the reference's tests (tests/tritium/test_rmsnorm.py:7-9, :76-235), cut down to rows
+    that keep the fixture small: a power-of-two width, an odd multiple of 8, the widest tested (11008), a
+    width below 512 (the reference's atomic dweight branch, not a multiple of the vector width) and one
+    just above it with >= 64 rows (its staged dweight branch)."""
+    cases = []
+    for dt in DTYPES:
+        for shape, h in (((16,), 1024), ((2, 3), 2560), ((3,), 11008), ((130,), 100), ((70,), 520)):
+            cases.append({"name": f"rms-{dt}-n{'x'.join(map(str, shape))}-h{h}", "shape": shape, "h": h, "dtype": dt})
+    return cases
+
+
+def make_rmsnorm_inputs(case: dict, index: int) -> dict:
+    g = torch.Generator(device="cpu").manual_seed(5000 + index)
+    dt = DTYPES[case["dtype"]]
+    shape = (*case["shape"], case["h"])
+    return {"x": torch.randn(shape, generator=g).to(dt), "residual": torch.randn(shape, generator=g).to(dt),
+            "weight": torch.randn(case["h"], generator=g).to(dt), "dy": torch.randn(shape, generator=g).to(dt),
+            "dres": torch.randn(shape, generator=g).to(dt), "eps": 1e-6}
+
+
+def dedup(rec: dict) -> dict:
+    """Store tensors that came out bit-identical once: a later key holds ("same_as", earlier key)."""
+    out: dict = {}
+    for key, val in rec.items():
+        twin = next((k for k, v in out.items() if torch.is_tensor(v) and v.shape == val.shape and v.dtype == val.dtype
+                     and torch.equal(v, val)), None)
+        out[key] = ("same_as", twin) if twin is not None else val
+    return out
+
+
+def fixture_tensor(rec: dict, key: str) -> torch.Tensor:
+    val = rec[key]
+    return rec[val[1]] if isinstance(val, tuple) else val
+
+
+def run_reference_rmsnorm(dest: str) -> None:
+    ref_dir = ROOT / "baseline" / "_ref"
+    sys.path.insert(0, str(ref_dir))
+    import tritium
+
+    dev = torch.device("cuda", 0)
+    out = {"_meta": {"torch": torch.__version__, "gpu": torch.cuda.get_device_name(0),
+                     "triton": __import__("triton").__version__}}
+    for i, case in enumerate(rmsnorm_case_list()):
+        inp = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in make_rmsnorm_inputs(case, i).items()}
+        x, r, w, dy, dres, eps = (inp[k] for k in ("x", "residual", "weight", "dy", "dres", "eps"))
+        rec = {"out": tritium.rmsnorm(x, w, eps).cpu()}
+        dx, dw = tritium.rmsnorm_backward(dy, x, w, eps)
+        rec["dx_direct"], rec["dweight_direct"] = dx.cpu(), dw.cpu()
+        xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        tritium.rmsnorm(xg, wg, eps).backward(dy)
+        rec["dx"], rec["dweight"] = xg.grad.cpu(), wg.grad.cpu()
+        o2, z2 = tritium.residual_rmsnorm(x, r, w, eps)
+        rec["res_out"], rec["res_z"] = o2.cpu(), z2.cpu()
+        xg, rg, wg = (t.clone().requires_grad_(True) for t in (x, r, w))
+        o3, z3 = tritium.residual_rmsnorm(xg, rg, wg, eps)
+        torch.autograd.backward([o3, z3], [dy, dres])
+        rec["res_dx"], rec["res_dresidual"], rec["res_dweight"] = xg.grad.cpu(), rg.grad.cpu(), wg.grad.cpu()
+        torch.cuda.synchronize()
+        print(case["name"], float(rec["out"].float().abs().mean()))
+        out[case["name"]] = dedup(rec)
+    torch.save(out, dest)
+    print(f"wrote {dest}")
 
 
 def input_checksums(inp: dict) -> dict:
@@ -150,8 +221,11 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--oracle", action="store_true")
     ap.add_argument("--reference", metavar="OUT")
+    ap.add_argument("--reference-rmsnorm", metavar="OUT")
     a = ap.parse_args()
     if a.oracle:
         run_oracle()
     if a.reference:
         run_reference(a.reference)
+    if a.reference_rmsnorm:
+        run_reference_rmsnorm(a.reference_rmsnorm)

@@ -121,7 +121,7 @@ def _fake_tritium():
         mod.linear_cross_entropy_backward = lambda *a: "reference backward"
         mod.cross_entropy = lambda *a: "reference plain forward"
         mod.cross_entropy_backward = lambda *a: "reference plain backward"
-        mod.rmsnorm = lambda *a: "another op"
+        mod.layernorm = lambda *a: "another op"
     root.ops = sub
     # on tritium.ops the attribute `cross_entropy` is the function (it shadows the submodule)
     for mod in (root, sub, leaf):
@@ -141,7 +141,7 @@ def test_install_rebinds_all_three_modules_and_uninstall_restores():
             assert mod.linear_cross_entropy_backward is ops.linear_cross_entropy_backward
             assert mod.cross_entropy is ce_ops.cross_entropy
             assert mod.cross_entropy_backward is ce_ops.cross_entropy_backward
-            assert mod.rmsnorm() == "another op"  # everything else is left alone
+            assert mod.layernorm() == "another op"  # everything else is left alone
         install(root)  # idempotent: the saved originals are not overwritten by our own functions
         uninstall(root)
         for mod in (root, sub, leaf):
@@ -166,6 +166,10 @@ def test_install_into_the_real_reference_package_if_present():
         install()
         assert tritium.linear_cross_entropy is ops.linear_cross_entropy
         assert sys.modules["tritium.ops.cross_entropy"].linear_cross_entropy_backward is ops.linear_cross_entropy_backward
+        from helion_b200 import norm_ops
+
+        assert tritium.residual_rmsnorm is norm_ops.residual_rmsnorm
+        assert sys.modules["tritium.ops.rmsnorm"].rmsnorm_backward is norm_ops.rmsnorm_backward
         with pytest.raises(ValueError, match="CUDA tensor"):
             tritium.linear_cross_entropy(torch.randn(4, 8), torch.randn(16, 8), torch.randint(16, (4,)))
         uninstall()
