@@ -7,7 +7,7 @@ forward 2 (read x, write out), residual forward 4 (x, residual in; out, residual
 (dy, x in; dx out), residual backward 4 (dy, dresidual, residual_out in; dz out). The reference's backward
 reads dy and x a second time for dweight; that extra traffic is not counted for either provider.
 
-    python -m benchmarks.bench_rmsnorm [--providers helion_b200,torch_eager,tritium]
+    python -m benchmarks.bench_rmsnorm [--providers helion_b200,torch_eager,tritium] [--shapes 16384x4096,...]
 """
 
 from __future__ import annotations
@@ -51,6 +51,7 @@ def _torch_backward(dy, x, w):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--providers", default="helion_b200,torch_eager,tritium")
+    ap.add_argument("--shapes", default="", help="comma-separated NxH (bf16) instead of the built-in list")
     args = ap.parse_args()
     require_cuda()
     peak = _hbm_peak()
@@ -58,7 +59,8 @@ def main() -> None:
     if "tritium" in args.providers and (ROOT / "baseline" / "_ref" / "tritium").exists():
         sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
         import tritium  # noqa: F811
-    for n, h in SHAPES + LARGE:
+    shapes = [tuple(int(v) for v in item.split("x")) for item in args.shapes.split(",") if item] or SHAPES + LARGE
+    for n, h in shapes:
         dtype = torch.float16 if (n, h) in SHAPES else torch.bfloat16
         x = torch.randn(n, h, device="cuda", dtype=dtype)
         r, dy, dz = torch.randn_like(x), torch.randn_like(x), torch.randn_like(x)

@@ -1283,18 +1283,25 @@ int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) 
 // shared memory, and as many stages (2..4) as fit.
 struct RmsRingPlan {
     int ctas_per_sm, stages;
+    int rows;  // rows per stage (RmsRingRows<vpt, n_streams>)
     size_t smem;
 };
 
-RmsRingPlan rms_ring_plan(const RmsShape& sh, long long H, int dtype, int n_streams) {
+RmsRingPlan rms_ring_plan(const RmsShape& sh, long long H, int dtype, int n_streams, bool forward) {
     RmsRingPlan p;
-    p.ctas_per_sm = 512 / sh.threads;
+    // threads per SM the registers allow: the forward kernels stay under 85 registers, the backward ones under 128
+    p.ctas_per_sm = (forward ? 768 : 512) / sh.threads;
     if (p.ctas_per_sm < 2) p.ctas_per_sm = 2;
     if (p.ctas_per_sm > 8) p.ctas_per_sm = 8;
-    const size_t stage = static_cast<size_t>(sh.rows) * n_streams * H * elem_size(dtype);
-    const size_t budget = kRmsRingBytesPerSm / p.ctas_per_sm - 2048;  // static shared memory and slack
-    long long st = static_cast<long long>(budget / stage);
-    p.stages = static_cast<int>(st > kRmsMaxStages ? kRmsMaxStages : st);
+    const int target = n_streams == 1 ? 8 : 4;
+    p.rows = sh.vpt >= target ? 1 : target / sh.vpt;
+    const size_t stage = static_cast<size_t>(p.rows) * n_streams * H * elem_size(dtype);
+    for (;; --p.ctas_per_sm) {  // fewer, larger rings until two stages fit
+        const size_t budget = kRmsRingBytesPerSm / p.ctas_per_sm - 2048;  // static shared memory and slack
+        const long long st = static_cast<long long>(budget / stage);
+        p.stages = static_cast<int>(st > kRmsMaxStages ? kRmsMaxStages : st);
+        if (p.stages >= 2 || p.ctas_per_sm == 2) break;
+    }
     p.smem = p.stages * stage;
     return p;
 }
@@ -1315,7 +1322,7 @@ int rms_ring_opt_in(const DeviceInfo& d) {
 int rms_ring_grid(const DeviceInfo& d, const RmsShape& sh, const RmsRingPlan& rp, long long n_rows, long long cap) {
     long long g = static_cast<long long>(d.sm_count) * rp.ctas_per_sm;
     if (cap > 0 && g > cap) g = cap;
-    const long long groups = cdiv(n_rows, sh.rows);
+    const long long groups = cdiv(n_rows, rp.rows);
     return static_cast<int>(groups < g ? groups : g);
 }
 
@@ -1331,7 +1338,7 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     T* rop = static_cast<T*>(residual_out);
     const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
     if (sh.vector && !sh.wide) {
-        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL ? 2 : 1);
+        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL ? 2 : 1, true);
         if (rp.stages >= 2) {
             const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);
             int rc = LCE_OK;
@@ -1415,8 +1422,8 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
             LCE_COUNT_LAUNCH();
             if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
         }
-    } else if (sh.vector && rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2).stages >= 2) {
-        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2);
+    } else if (sh.vector && rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2, false).stages >= 2) {
+        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2, false);
         const int grid = rms_ring_grid(d, sh, rp, n_rows, kRmsMaxPartials);
         n_partials = grid;
         int rc = LCE_OK;

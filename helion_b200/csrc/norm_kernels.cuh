@@ -45,20 +45,59 @@ __device__ __forceinline__ uint4 rms_load(const T* __restrict__ row, int c, int 
     }
 }
 
+// 16-byte vector <-> floats. The 16-bit forms convert two elements per instruction where the hardware
+// can (bf16 -> fp32 is a shift or a mask of the packed word; fp32 -> 16-bit pairs is one cvt).
 template <class T>
 __device__ __forceinline__ void rms_unpack(const uint4& raw, float (&v)[RmsTile<T>::kVec]) {
-    alignas(16) T tmp[RmsTile<T>::kVec];
-    *reinterpret_cast<uint4*>(tmp) = raw;
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    if constexpr (std::is_same<T, float>::value) {
 #pragma unroll
-    for (int j = 0; j < RmsTile<T>::kVec; ++j) v[j] = Cvt<T>::to_f(tmp[j]);
+        for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(w[j]);
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    }
 }
 
 template <class T>
 __device__ __forceinline__ uint4 rms_pack(const float (&v)[RmsTile<T>::kVec]) {
-    alignas(16) T tmp[RmsTile<T>::kVec];
+    uint32_t w[4];
+    if constexpr (std::is_same<T, float>::value) {
 #pragma unroll
-    for (int j = 0; j < RmsTile<T>::kVec; ++j) tmp[j] = Cvt<T>::from_f(v[j]);
-    return *reinterpret_cast<const uint4*>(tmp);
+        for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(v[j]);
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// 1 / sqrt(ss / H + eps) from a precomputed 1 / H: the hardware reciprocal square root plus one Newton
+// step (relative error ~1e-7) - an exactly rounded divide and square root would cost every thread more
+// instructions than the rest of its row.
+__device__ __forceinline__ float rms_rstd(float ss, float inv_h, float eps) {
+    const float a = fmaf(ss, inv_h, eps);
+    const float y = rsqrtf(a);
+    return y * fmaf(-0.5f * a * y, y, 1.5f);
 }
 
 template <class T, bool VECTOR>
@@ -75,25 +114,29 @@ __device__ __forceinline__ void rms_store(T* __restrict__ row, int c, int H, con
     }
 }
 
-// Sums NV values over the CTA; every thread gets the totals. Warp shuffles, then the warp totals in
-// warp order - a fixed order, so the result does not depend on timing. `red` holds NV x 32 floats and
-// must not be reused before the next __syncthreads() (callers alternate two buffers).
+// Sums NV values (NV a power of two <= 32) over a CTA of at most 32 warps; every thread gets the totals.
+// Warp shuffles, then the warp totals through shared memory: lane l picks up the partials p = l, l + 32,
+// ... (p = warp * NV + value), a strided xor butterfly leaves the total of value l % NV in lane l, and NV
+// broadcasts hand every lane all of them. The order is fixed, so the result does not depend on
+// timing. `red` holds 32 x NV floats and must not be reused before the next __syncthreads() (callers
+// alternate two buffers).
 template <int NV>
 __device__ __forceinline__ void rms_block_sum(float (&v)[NV], float* red) {
+    static_assert(NV >= 1 && NV <= 32 && (NV & (NV - 1)) == 0, "power of two");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
-        if (lane == 0) red[i * 32 + warp] = v[i];
+        if (lane == 0) red[warp * NV + i] = v[i];
     }
     __syncthreads();
+    float part = 0.f;
+    for (int p = lane; p < n_warps * NV; p += 32) part += red[p];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        float s = 0.f;
-        for (int w = 0; w < n_warps; ++w) s += red[i * 32 + w];
-        v[i] = s;
-    }
+    for (int o = NV; o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = __shfl_sync(0xffffffffu, part, i);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -113,6 +156,7 @@ __global__ void __launch_bounds__(kRmsMaxThreads)
 rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                    T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
                    int n_rows, int H, float eps) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     constexpr int VEC = RmsTile<T>::kVec;
     constexpr int ROWS = RmsRows<VPT>::kRows;
     __shared__ float red[2][ROWS * 32];
@@ -162,7 +206,7 @@ rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
         for (int r = 0; r < ROWS; ++r) {
             const long long off = static_cast<long long>(row0 + r) * H;
             const int h = row0 + r < n_rows ? H : 0;
-            const float rstd = 1.0f / sqrtf(ss[r] / static_cast<float>(H) + eps);
+            const float rstd = rms_rstd(ss[r], inv_h, eps);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 float z[VEC], w[VEC];
@@ -196,6 +240,15 @@ rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
 // Waits on the mbarriers are bounded; on a timeout the CTA records kDevErrNormTimeout in the device
 // status word, drains what it issued (bounded again) and returns.
 // ---------------------------------------------------------------------------------------------
+// Rows per stage: enough that the per-stage costs (barriers, the cross-warp sum) are spread over
+// 8 vectors per thread when one tensor streams in, 4 when two or three do (the stage must stay small
+// enough for a multi-stage ring).
+template <int VPT, int NS>
+struct RmsRingRows {
+    static constexpr int kTarget = NS == 1 ? 8 : 4;
+    static constexpr int kRows = VPT >= kTarget ? 1 : kTarget / VPT;
+};
+
 constexpr int kRmsMaxStages = 4;
 constexpr int kRmsRingBytesPerSm = 200 * 1024;
 constexpr int kDevErrNormTimeout = 111;
@@ -228,7 +281,7 @@ __device__ __forceinline__ void rms_ring_issue(RmsRing& ring, unsigned char* dat
 // After a timeout: thread 0 waits (bounded) for the loads that were issued but never consumed, so that
 // no copy is still writing into this CTA's shared memory when it exits.
 __device__ __forceinline__ void rms_ring_drain(RmsRing& ring, int k_next, int stages, long long n_groups, int* status) {
-    atomicCAS(status, 0, kDevErrNormTimeout);
+    if (status != nullptr) atomicCAS(status, 0, kDevErrNormTimeout);
     ring.drain_flag = 0;
     for (int k = k_next; k < k_next + stages; ++k) {
         if (blockIdx.x + static_cast<long long>(k) * gridDim.x >= n_groups) break;
@@ -241,9 +294,11 @@ __global__ void __launch_bounds__(kRmsMaxThreads, 2)
 rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                         T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
                         int n_rows, int H, float eps, int stages, int* __restrict__ status) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     constexpr int VEC = RmsTile<T>::kVec;
-    constexpr int ROWS = RmsRows<VPT>::kRows;
     constexpr int NS = RESIDUAL ? 2 : 1;
+    constexpr int ROWS = RmsRingRows<VPT, NS>::kRows;
+    constexpr bool kWeightUnpacked = VPT * VEC <= 16;  // else kept packed and unpacked per use
     extern __shared__ __align__(128) unsigned char ring_data[];
     __shared__ RmsRing ring;
     __shared__ float red[2][ROWS * 32];
@@ -258,9 +313,14 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
         ptx::fence_mbar_init();
         for (int k = 0; k < stages; ++k) rms_ring_issue<T, ROWS, NS>(ring, ring_data, srcs, k, stages, n_rows, H);
     }
-    uint4 wraw[VPT];  // this thread's weight columns
+    uint4 wraw[kWeightUnpacked ? 1 : VPT];  // this thread's weight columns
+    float wf[kWeightUnpacked ? VPT : 1][VEC];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) wraw[i] = rms_load<T, true>(weight, (i * blockDim.x + t) * VEC, H);
+    for (int i = 0; i < VPT; ++i) {
+        const uint4 raw = rms_load<T, true>(weight, (i * blockDim.x + t) * VEC, H);
+        if (kWeightUnpacked) rms_unpack<T>(raw, wf[i]);
+        else wraw[i] = raw;
+    }
     __syncthreads();
 
     int k = 0;
@@ -304,7 +364,7 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             if (row0 + r < n_rows) {
-                const float rstd = 1.0f / sqrtf(ss[r] / static_cast<float>(H) + eps);
+                const float rstd = rms_rstd(ss[r], inv_h, eps);
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int c = (i * blockDim.x + t) * VEC;
@@ -317,9 +377,9 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
 #pragma unroll
                             for (int j = 0; j < VEC; ++j) z[j] += q[j];
                         }
-                        rms_unpack<T>(wraw[i], w);
+                        if (!kWeightUnpacked) rms_unpack<T>(wraw[i], w);
 #pragma unroll
-                        for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * w[j];
+                        for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * (kWeightUnpacked ? wf[i][j] : w[j]);
                         *reinterpret_cast<uint4*>(out + (row0 + r) * H + c) = rms_pack<T>(z);
                     }
                 }
@@ -343,9 +403,10 @@ rms_ring_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
                          const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
                          float* __restrict__ partial, int n_rows, int H, float eps, int stages,
                          int* __restrict__ status) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     constexpr int VEC = RmsTile<T>::kVec;
-    constexpr int ROWS = RmsRows<VPT>::kRows;
     constexpr int NS = DRES ? 3 : 2;
+    constexpr int ROWS = RmsRingRows<VPT, NS>::kRows;
     constexpr bool kWeightInRegs = VPT * VEC <= 16;
     extern __shared__ __align__(128) unsigned char ring_data[];
     __shared__ RmsRing ring;
@@ -418,8 +479,9 @@ rms_ring_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
         for (int r = 0; r < ROWS; ++r) {
             if (row0 + r < n_rows) {
                 const float rstd = rstd_in != nullptr ? rstd_in[row0 + r]
-                                                      : 1.0f / sqrtf(sums[2 * r + 1] / static_cast<float>(H) + eps);
-                const float coef = rstd * rstd * rstd / static_cast<float>(H);
+                                                      : rms_rstd(sums[2 * r + 1], inv_h, eps);
+                // dx = rstd * w * dy - (rstd^3 / H * c) * x, two scalars per row hoisted out of the columns
+                const float coefc = rstd * rstd * rstd * inv_h * sums[2 * r];
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int c = (i * blockDim.x + t) * VEC;
@@ -432,7 +494,7 @@ rms_ring_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 #pragma unroll
                         for (int j = 0; j < VEC; ++j) {
                             dwacc[i][j] = fmaf(d[j] * xv[j], rstd, dwacc[i][j]);
-                            o[j] = rstd * (d[j] * w[j]) - coef * xv[j] * sums[2 * r];
+                            o[j] = fmaf(rstd * w[j], d[j], -coefc * xv[j]);
                         }
                         if (DRES) {
                             float q[VEC];
@@ -473,6 +535,7 @@ __global__ void __launch_bounds__(kRmsMaxThreads)
 rms_forward_wide_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
                         T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
                         int n_rows, int H, float eps) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     __shared__ float red[2][32];
     int it = 0;
     for (int row = blockIdx.x; row < n_rows; row += gridDim.x, ++it) {
@@ -487,7 +550,7 @@ rms_forward_wide_kernel(const T* __restrict__ x, const T* __restrict__ residual,
             ss[0] = fmaf(z, z, ss[0]);
         }
         rms_block_sum<1>(ss, red[it & 1]);
-        const float rstd = 1.0f / sqrtf(ss[0] / static_cast<float>(H) + eps);
+        const float rstd = rms_rstd(ss[0], inv_h, eps);
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
             float z = Cvt<T>::to_f(x[off + c]);
             if (RESIDUAL) z += Cvt<T>::to_f(residual[off + c]);
@@ -509,6 +572,7 @@ __global__ void __launch_bounds__(kRmsMaxThreads)
 rms_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ weight,
                     const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
                     float* __restrict__ partial, int n_rows, int H, float eps) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     constexpr int VEC = RmsTile<T>::kVec;
     constexpr int ROWS = RmsRows<VPT>::kRows;
     constexpr bool kWeightInRegs = VPT * VEC <= 16;  // wider rows re-read the weights (L1 hits) every step
@@ -570,8 +634,8 @@ rms_backward_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
             float rstd = 0.f;  // a row past the end adds nothing to dweight
             if (h != 0)
                 rstd = rstd_in != nullptr ? rstd_in[row0 + r]
-                                          : 1.0f / sqrtf(sums[2 * r + 1] / static_cast<float>(H) + eps);
-            const float coef = rstd * rstd * rstd / static_cast<float>(H);
+                                          : rms_rstd(sums[2 * r + 1], inv_h, eps);
+            const float coef = rstd * rstd * rstd * inv_h;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int c = (i * blockDim.x + t) * VEC;
@@ -614,6 +678,7 @@ __global__ void __launch_bounds__(kRmsMaxThreads)
 rms_backward_wide_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ weight,
                          const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
                          float* __restrict__ rstd_ws, int n_rows, int H, float eps) {
+    const float inv_h = 1.0f / static_cast<float>(H);
     __shared__ float red[2][64];
     int it = 0;
     for (int row = blockIdx.x; row < n_rows; row += gridDim.x, ++it) {
@@ -626,8 +691,8 @@ rms_backward_wide_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
             sums[1] = fmaf(xv, xv, sums[1]);
         }
         rms_block_sum<2>(sums, red[it & 1]);
-        const float rstd = rstd_in != nullptr ? rstd_in[row] : 1.0f / sqrtf(sums[1] / static_cast<float>(H) + eps);
-        const float coef = rstd * rstd * rstd / static_cast<float>(H);
+        const float rstd = rstd_in != nullptr ? rstd_in[row] : rms_rstd(sums[1], inv_h, eps);
+        const float coef = rstd * rstd * rstd * inv_h;
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
             const float xv = Cvt<T>::to_f(x[off + c]);
             const float wd = Cvt<T>::to_f(dy[off + c]) * Cvt<T>::to_f(weight[c]);
