@@ -1281,6 +1281,8 @@ int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) 
 
 // Shared-memory ring of a ring kernel: CTAs per SM by thread count, the per-CTA share of the SM's
 // shared memory, and as many stages (2..4) as fit.
+constexpr long long kRmsRingMinBytes = 16ll << 20;  // forward only; the backward ring wins at every size measured
+
 struct RmsRingPlan {
     int ctas_per_sm, stages;
     int rows;  // rows per stage (RmsRingRows<vpt, n_streams>)
@@ -1337,7 +1339,9 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     T* op = static_cast<T*>(out);
     T* rop = static_cast<T*>(residual_out);
     const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
-    if (sh.vector && !sh.wide) {
+    // The ring pays ~2 us of set-up (barrier init, first copies) and earns it back only when every SM streams
+    // many rows; below kRmsRingMinBytes of input the register-resident kernel finishes sooner.
+    if (sh.vector && !sh.wide && n_rows * H * static_cast<long long>(sizeof(T)) * (RESIDUAL ? 2 : 1) >= kRmsRingMinBytes) {
         const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL ? 2 : 1, true);
         if (rp.stages >= 2) {
             const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);

@@ -114,22 +114,38 @@ __device__ __forceinline__ void rms_store(T* __restrict__ row, int c, int H, con
     }
 }
 
+template <int N> struct RmsLog2 { static constexpr int value = 1 + RmsLog2<N / 2>::value; };
+template <> struct RmsLog2<1> { static constexpr int value = 0; };
+
 // Sums NV values (NV a power of two <= 32) over a CTA of at most 32 warps; every thread gets the totals.
-// Warp shuffles, then the warp totals through shared memory: lane l picks up the partials p = l, l + 32,
-// ... (p = warp * NV + value), a strided xor butterfly leaves the total of value l % NV in lane l, and NV
-// broadcasts hand every lane all of them. The order is fixed, so the result does not depend on
-// timing. `red` holds 32 x NV floats and must not be reused before the next __syncthreads() (callers
-// alternate two buffers).
+//  1. inside a warp, a transposed butterfly: at each of the first log2(NV) steps a lane keeps half of its
+//     values and trades the other half with its partner, so NV values cost NV - 1 + (5 - log2 NV) shuffles
+//     instead of 5 NV; lane l ends up with the warp total of value l >> (5 - log2 NV);
+//  2. the warp totals go through shared memory: lane l picks up the partials p = l, l + 32, ...
+//     (p = warp * NV + value), a strided butterfly leaves the total of value l % NV in lane l, and NV
+//     broadcasts hand every lane all of them.
+// The order of the additions is fixed, so the result does not depend on timing. `red` holds 32 x NV floats
+// and must not be reused before the next __syncthreads() (callers alternate two buffers).
 template <int NV>
 __device__ __forceinline__ void rms_block_sum(float (&v)[NV], float* red) {
     static_assert(NV >= 1 && NV <= 32 && (NV & (NV - 1)) == 0, "power of two");
+    constexpr int L = RmsLog2<NV>::value;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
+    for (int s = 0; s < L; ++s) {
+        const int o = 16 >> s, half = NV >> (s + 1);
+        const bool upper = (lane & o) != 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
-        if (lane == 0) red[warp * NV + i] = v[i];
+        for (int i = 0; i < half; ++i) {
+            const float send = upper ? v[i] : v[i + half];
+            const float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
     }
+    float r = v[0];
+#pragma unroll
+    for (int s = L; s < 5; ++s) r += __shfl_xor_sync(0xffffffffu, r, 16 >> s);
+    if ((lane & ((32 >> L) - 1)) == 0) red[warp * NV + (lane >> (5 - L))] = r;
     __syncthreads();
     float part = 0.f;
     for (int p = lane; p < n_warps * NV; p += 32) part += red[p];

@@ -178,6 +178,24 @@ def test_odd_widths_and_the_wide_path(dtype, shape):
     close(dw, ref_dw, accumulated=True)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden_size", [1024, 2560, 5120, 11008])
+def test_forward_ring_kernels(dtype, hidden_size):
+    """The forward takes the shared-memory ring only from 16 MiB of input: one case per dtype and
+    vectors-per-thread variant, with a row count that leaves the last row group partial."""
+    elem = torch.empty((), dtype=dtype).element_size()
+    n_rows = (16 << 20) // (hidden_size * elem) + 3
+    x = torch.randn(n_rows, hidden_size, device=DEV, dtype=dtype)
+    r = torch.randn_like(x)
+    w = torch.randn(hidden_size, device=DEV, dtype=dtype)
+    ulp_close(helion_b200.rmsnorm(x, w), fwd_ref(x, w), 2)
+    ref = oracle.restated_rmsnorm_forward(x.cpu(), w.cpu(), 1e-6, residual=r.cpu())
+    half = n_rows // 2 + 1  # residual form: two tensors stream in, so half the rows reach the threshold
+    out, z = helion_b200.residual_rmsnorm(x[:half].contiguous(), r[:half].contiguous(), w)
+    assert torch.equal(z.cpu(), ref["residual_out"][:half])
+    ulp_close(out, ref["out"][:half], 2)
+
+
 def test_unaligned_base_pointers_take_the_element_path():
     buf = torch.randn(3 * 1024 + 1, device=DEV, dtype=torch.bfloat16)
     x = buf[1:].view(3, 1024)  # 2 bytes past a 16-byte boundary
