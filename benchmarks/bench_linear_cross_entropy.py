@@ -11,7 +11,7 @@ Providers: ``helion_b200`` (this repository), ``torch_eager`` (F.linear + F.cros
 the logits fit), ``tritium`` (the reference's own Triton/cuBLAS op, only if a copy is installed under
 baseline/_ref). One JSON object per line on stdout.
 
-    python -m benchmarks.bench_linear_cross_entropy [--configs] [--shapes] [--providers a,b]
+    python -m benchmarks.bench_linear_cross_entropy [--configs] [--shapes] [--sweep] [--fp32] [--providers a,b]
 """
 
 from __future__ import annotations
@@ -41,6 +41,7 @@ SHAPES = [
     (512, 4096, 128256),
     (1024, 4096, 32000),
 ]
+FP32_SHAPES = [(512, 1024, 8192), (2048, 1024, 32768), (4096, 2048, 32000)]  # CUDA-core path (no TF32)
 CONFIG_NAMES = ["gpt2-small", "llama3-8b", "large-vocab"]
 SWEEP_ROWS = [1024, 4096, 16384, 65536]
 
@@ -127,13 +128,21 @@ def main() -> None:
     ap.add_argument("--shapes", action="store_true", help="the reference harness's seven fp16 shapes")
     ap.add_argument("--configs", action="store_true", help="the benchmark head configurations (bf16)")
     ap.add_argument("--sweep", action="store_true", help="Llama-3 head, N in {1024, 4096, 16384, 65536}")
+    ap.add_argument("--fp32", action="store_true", help="fp32 inputs: the CUDA-core GEMM path, three shapes")
     ap.add_argument("--providers", default="helion_b200,torch_eager,tritium")
     args = ap.parse_args()
     require_cuda()
     providers = args.providers.split(",")
     peak = _peak()
-    if not (args.shapes or args.configs or args.sweep):
+    if not (args.shapes or args.configs or args.sweep or args.fp32):
         args.shapes = args.configs = True
+    if args.fp32:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        for n, h, v in FP32_SHAPES:
+            hidden = torch.randn(n, h, device="cuda")
+            weight = torch.randn(v, h, device="cuda") * 0.05
+            target = torch.randint(v, (n,), device="cuda")
+            time_case(f"fp32-{n}x{h}x{v}", hidden, weight, target, providers, peak)
     if args.shapes:
         for n, h, v in SHAPES:
             hidden = torch.randn(n, h, device="cuda", dtype=torch.float16)

@@ -26,7 +26,7 @@ constexpr int kSimtThreads = 256;
 constexpr int kSimtPitch = 128 + 4;   // operand tiles [k][mn] in floats: rows stay 16-byte aligned, the pad
                                       // spreads a k-contiguous deposit over the banks
 constexpr int kSimtCPitch = 64 + 4;   // one 64-column half of the C tile
-constexpr int kSimtLoads = 128 * kSimtBK / kSimtThreads;  // 8 elements of each operand per thread and k step
+constexpr int kSimtLoads = 128 * kSimtBK / kSimtThreads;  // 4 elements of each operand per thread and k step
 static_assert(kBM == 128, "the thread layout below is written for 128 x 128 tiles");
 
 template <class T>
@@ -37,41 +37,95 @@ struct SimtOperand {
     int extent_mn;        // valid m (resp. n)
 };
 
-// One thread's share of a (128 x 16) operand tile: element i sits at (mn_t + i * mn_step,
-// k_t + i * k_step) of the tile, chosen so that consecutive threads walk the contiguous direction
-// of the operand in global memory.
-struct SimtLane {
-    int mn_t, k_t, mn_step, k_step;
-};
+// How a thread fetches its share (4 elements) of a 128 x 8 operand tile:
+//   kSimtGeneric  four scalar loads with run-time strides and per-element bounds tests: any dtype,
+//                 any alignment, any majorness (consecutive threads walk the contiguous direction);
+//   kSimtVecK     fp32, k contiguous: one 16-byte load of 4 consecutive k of one row (thread t: row t/2,
+//                 k 4*(t%2)), deposited as four conflict-free scalar stores (the tile is [k][mn]);
+//   kSimtVecMN    fp32, m/n contiguous: one 16-byte load of 4 consecutive m/n at one k (thread t: k t/32,
+//                 m/n 4*(t%32)), deposited as one 16-byte store.
+// The vector modes need a 16-byte aligned base, strides and the vectorised extent in multiples of 4;
+// the host picks them (launch_simt). Row validity is settled once per tile, and the pointer just advances.
+enum SimtMode { kSimtGeneric = 0, kSimtVecK = 1, kSimtVecMN = 2 };
 
-__device__ __forceinline__ SimtLane simt_lane(bool k_contiguous, int t) {
-    SimtLane l;
-    if (k_contiguous) { l.k_t = t % kSimtBK; l.mn_t = t / kSimtBK; l.mn_step = kSimtThreads / kSimtBK; l.k_step = 0; }
-    else { l.mn_t = t % 128; l.k_t = t / 128; l.mn_step = 0; l.k_step = kSimtThreads / 128; }
-    return l;
-}
+template <class T, int MODE>
+struct SimtLoader;
 
 template <class T>
-__device__ __forceinline__ void simt_fetch(const SimtOperand<T>& op, const SimtLane& l, int mn0, int k0, int k_end,
-                                           float (&r)[kSimtLoads]) {
-    const T* p = op.ptr + static_cast<long long>(mn0 + l.mn_t) * op.stride_mn +
-                 static_cast<long long>(k0 + l.k_t) * op.stride_k;
-    const long long step = l.mn_step * op.stride_mn + l.k_step * op.stride_k;
-#pragma unroll
-    for (int i = 0; i < kSimtLoads; ++i) {
-        r[i] = 0.f;
-        if (mn0 + l.mn_t + i * l.mn_step < op.extent_mn && k0 + l.k_t + i * l.k_step < k_end)
-            r[i] = Cvt<T>::to_f(p[i * step]);
+struct SimtLoader<T, kSimtGeneric> {
+    const T* p;
+    long long step, k_adv;
+    int mn_t, k_t, mn_step, k_step, mn_left;
+    __device__ __forceinline__ void init(const SimtOperand<T>& op, int mn0, int k_begin, int t) {
+        if (op.stride_k == 1) { k_t = t % kSimtBK; mn_t = t / kSimtBK; mn_step = kSimtThreads / kSimtBK; k_step = 0; }
+        else { mn_t = t % 128; k_t = t / 128; mn_step = 0; k_step = kSimtThreads / 128; }
+        p = op.ptr + static_cast<long long>(mn0 + mn_t) * op.stride_mn + static_cast<long long>(k_begin + k_t) * op.stride_k;
+        step = mn_step * op.stride_mn + k_step * op.stride_k;
+        k_adv = kSimtBK * op.stride_k;
+        mn_left = op.extent_mn - mn0 - mn_t;  // element i is in range iff i * mn_step < mn_left
     }
-}
-
-__device__ __forceinline__ void simt_deposit(float* tile, const SimtLane& l, const float (&r)[kSimtLoads]) {
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
 #pragma unroll
-    for (int i = 0; i < kSimtLoads; ++i)
-        tile[(l.k_t + i * l.k_step) * kSimtPitch + l.mn_t + i * l.mn_step] = r[i];
-}
+        for (int i = 0; i < kSimtLoads; ++i) {
+            r[i] = 0.f;
+            if (i * mn_step < mn_left && k0 + k_t + i * k_step < k_end) r[i] = Cvt<T>::to_f(p[i * step]);
+        }
+        p += k_adv;
+    }
+    __device__ __forceinline__ void deposit(float* tile, const float (&r)[kSimtLoads]) const {
+#pragma unroll
+        for (int i = 0; i < kSimtLoads; ++i) tile[(k_t + i * k_step) * kSimtPitch + mn_t + i * mn_step] = r[i];
+    }
+};
 
-template <class T, class Epi>
+template <>
+struct SimtLoader<float, kSimtVecK> {
+    const float* p;
+    int row, k4;
+    bool valid;
+    __device__ __forceinline__ void init(const SimtOperand<float>& op, int mn0, int k_begin, int t) {
+        row = t >> 1;
+        k4 = (t & 1) * 4;
+        valid = mn0 + row < op.extent_mn;
+        p = op.ptr + static_cast<long long>(mn0 + row) * op.stride_mn + k_begin + k4;
+    }
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid && k0 + k4 < k_end) v = *reinterpret_cast<const float4*>(p);  // K % 4 == 0: all four or none
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+        p += kSimtBK;
+    }
+    __device__ __forceinline__ void deposit(float* tile, const float (&r)[kSimtLoads]) const {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tile[(k4 + j) * kSimtPitch + row] = r[j];
+    }
+};
+
+template <>
+struct SimtLoader<float, kSimtVecMN> {
+    const float* p;
+    long long k_adv;
+    int k, mn4;
+    bool valid;
+    __device__ __forceinline__ void init(const SimtOperand<float>& op, int mn0, int k_begin, int t) {
+        k = t >> 5;
+        mn4 = (t & 31) * 4;
+        valid = mn0 + mn4 < op.extent_mn;  // extent % 4 == 0: all four or none
+        p = op.ptr + (mn0 + mn4) + static_cast<long long>(k_begin + k) * op.stride_k;
+        k_adv = kSimtBK * op.stride_k;
+    }
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid && k0 + k < k_end) v = *reinterpret_cast<const float4*>(p);
+        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+        p += k_adv;
+    }
+    __device__ __forceinline__ void deposit(float* tile, const float (&r)[kSimtLoads]) const {
+        *reinterpret_cast<float4*>(tile + k * kSimtPitch + mn4) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+};
+
+template <class T, class Epi, int AMODE = kSimtGeneric, int BMODE = kSimtGeneric>
 __global__ void __launch_bounds__(kSimtThreads, 2)
 gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_tiles, int k_splits,
                  const typename Epi::Params ep) {
@@ -82,7 +136,7 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
 
     const int t = threadIdx.x;
     const int ty = t >> 4, tx = t & 15;
-    const SimtLane la = simt_lane(A.stride_k == 1, t), lb = simt_lane(B.stride_k == 1, t);
+    static_assert(kSimtLoads == 4, "the vector loaders move one 16-byte vector per thread");
     // k_splits > 1: work item = (tile, slice of the contraction); the epilogue stores slices side by side
     // (kStoreSlice) and splitk_reduce_kernel adds them in slice order.
     const int total_tiles = m_tiles * n_tiles;
@@ -103,18 +157,22 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
+        SimtLoader<T, AMODE> la;
+        SimtLoader<T, BMODE> lb;
+        la.init(A, m0, k_begin, t);
+        lb.init(B, n0, k_begin, t);
         float ra[kSimtLoads], rb[kSimtLoads];
-        simt_fetch<T>(A, la, m0, k_begin, k_end, ra);
-        simt_fetch<T>(B, lb, n0, k_begin, k_end, rb);
-        simt_deposit(smem, la, ra);
-        simt_deposit(smem + kTileFloats, lb, rb);
+        la.fetch(k_begin, k_end, ra);
+        lb.fetch(k_begin, k_end, rb);
+        la.deposit(smem, ra);
+        lb.deposit(smem + kTileFloats, rb);
         __syncthreads();
         int cur = 0;
         for (int k0 = k_begin; k0 < k_end; k0 += kSimtBK) {
             const bool more = k0 + kSimtBK < k_end;
             if (more) {  // in flight while this step multiplies
-                simt_fetch<T>(A, la, m0, k0 + kSimtBK, k_end, ra);
-                simt_fetch<T>(B, lb, n0, k0 + kSimtBK, k_end, rb);
+                la.fetch(k0 + kSimtBK, k_end, ra);
+                lb.fetch(k0 + kSimtBK, k_end, rb);
             }
             const float* As = smem + cur * 2 * kTileFloats;
             const float* Bs = As + kTileFloats;
@@ -133,8 +191,8 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
             }
             if (more) {
                 float* nxt = smem + (cur ^ 1) * 2 * kTileFloats;
-                simt_deposit(nxt, la, ra);
-                simt_deposit(nxt + kTileFloats, lb, rb);
+                la.deposit(nxt, ra);
+                lb.deposit(nxt + kTileFloats, rb);
             }
             __syncthreads();
             cur ^= 1;

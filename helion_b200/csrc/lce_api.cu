@@ -234,8 +234,26 @@ int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool
     const long long cap = static_cast<long long>(d.sm_count) * 4;
     const long long work = m_tiles * n_tiles * k_splits;
     const int grid = static_cast<int>(work < cap ? work : cap);
-    gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(
-        A, B, static_cast<int>(K), static_cast<int>(m_tiles), static_cast<int>(n_tiles), k_splits, ep);
+    const int k = static_cast<int>(K), mt = static_cast<int>(m_tiles), nt = static_cast<int>(n_tiles);
+    bool launched = false;
+    if constexpr (std::is_same<T, float>::value) {
+        // fp32 operands that allow 16-byte loads along their contiguous direction take the vector loaders
+        const auto mode = [&](const SimtOperand<float>& op, long long extent) {
+            if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0) return static_cast<int>(kSimtGeneric);
+            if (op.stride_k == 1 && op.stride_mn % 4 == 0 && K % 4 == 0) return static_cast<int>(kSimtVecK);
+            if (op.stride_mn == 1 && op.stride_k % 4 == 0 && extent % 4 == 0) return static_cast<int>(kSimtVecMN);
+            return static_cast<int>(kSimtGeneric);
+        };
+        const int am = mode(A, M), bm = mode(B, Nn);
+#define LCE_SIMT_GO(AM, BM) \
+    gemm_simt_kernel<float, Epi, AM, BM><<<grid, kSimtThreads, 0, stream>>>(A, B, k, mt, nt, k_splits, ep), launched = true
+        if (am == kSimtVecK && bm == kSimtVecK) LCE_SIMT_GO(kSimtVecK, kSimtVecK);
+        else if (am == kSimtVecK && bm == kSimtVecMN) LCE_SIMT_GO(kSimtVecK, kSimtVecMN);
+        else if (am == kSimtVecMN && bm == kSimtVecK) LCE_SIMT_GO(kSimtVecMN, kSimtVecK);
+        else if (am == kSimtVecMN && bm == kSimtVecMN) LCE_SIMT_GO(kSimtVecMN, kSimtVecMN);
+#undef LCE_SIMT_GO
+    }
+    if (!launched) gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(A, B, k, mt, nt, k_splits, ep);
     LCE_COUNT_LAUNCH();
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
