@@ -1300,6 +1300,7 @@ int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) 
 // Shared-memory ring of a ring kernel: CTAs per SM by thread count, the per-CTA share of the SM's
 // shared memory, and as many stages (2..4) as fit.
 constexpr long long kRmsRingMinBytes = 16ll << 20;  // forward only; the backward ring wins at every size measured
+constexpr long long kRmsRingMinRowBytes = 8192;
 
 struct RmsRingPlan {
     int ctas_per_sm, stages;
@@ -1309,8 +1310,14 @@ struct RmsRingPlan {
 
 RmsRingPlan rms_ring_plan(const RmsShape& sh, long long H, int dtype, int n_streams, bool forward) {
     RmsRingPlan p;
+    // tuning knobs: HELION_B200_RMS_CTAS = CTAs per SM, HELION_B200_RMS_STAGES = most stages per ring
+    static const int kCtasOverride = [] { const char* e = getenv("HELION_B200_RMS_CTAS"); return e ? atoi(e) : 0; }();
+    static const int kStagesCap = [] {
+        const char* e = getenv("HELION_B200_RMS_STAGES");
+        return e && atoi(e) >= 2 && atoi(e) <= kRmsMaxStages ? atoi(e) : kRmsMaxStages;
+    }();
     // threads per SM the registers allow: the forward kernels stay under 85 registers, the backward ones under 128
-    p.ctas_per_sm = (forward ? 768 : 512) / sh.threads;
+    p.ctas_per_sm = kCtasOverride > 0 ? kCtasOverride : (forward ? 768 : 512) / sh.threads;
     if (p.ctas_per_sm < 2) p.ctas_per_sm = 2;
     if (p.ctas_per_sm > 8) p.ctas_per_sm = 8;
     const int target = n_streams == 1 ? 8 : 4;
@@ -1319,7 +1326,7 @@ RmsRingPlan rms_ring_plan(const RmsShape& sh, long long H, int dtype, int n_stre
     for (;; --p.ctas_per_sm) {  // fewer, larger rings until two stages fit
         const size_t budget = kRmsRingBytesPerSm / p.ctas_per_sm - 2048;  // static shared memory and slack
         const long long st = static_cast<long long>(budget / stage);
-        p.stages = static_cast<int>(st > kRmsMaxStages ? kRmsMaxStages : st);
+        p.stages = static_cast<int>(st > kStagesCap ? kStagesCap : st);
         if (p.stages >= 2 || p.ctas_per_sm == 2) break;
     }
     p.smem = p.stages * stage;
@@ -1352,29 +1359,33 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
                        long long H, float eps, cudaStream_t s) {
     const T* xp = static_cast<const T*>(x);
     const T* rp = static_cast<const T*>(residual);
-    const T* rp_src = rp;
     const T* wp = static_cast<const T*>(weight);
     T* op = static_cast<T*>(out);
     T* rop = static_cast<T*>(residual_out);
     const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
-    // The ring pays ~2 us of set-up (barrier init, first copies) and earns it back only when every SM streams
-    // many rows; below kRmsRingMinBytes of input the register-resident kernel finishes sooner.
-    if (sh.vector && !sh.wide && n_rows * H * static_cast<long long>(sizeof(T)) * (RESIDUAL ? 2 : 1) >= kRmsRingMinBytes) {
-        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL ? 2 : 1, true);
+    // Plain rmsnorm of rows of 8 KB and more streams through the shared-memory ring once the input reaches
+    // kRmsRingMinBytes; narrower rows, small inputs and the residual form are faster on the register kernels
+    // (measured: the ring's set-up costs ~2 us, and with two tensors streaming in it gains nothing).
+    static const long long kRingMinBytes = [] {  // HELION_B200_RMS_RING_MIN_MB overrides (tuning knob)
+        const char* e = getenv("HELION_B200_RMS_RING_MIN_MB");
+        return e ? atoll(e) << 20 : kRmsRingMinBytes;
+    }();
+    const long long row_bytes = H * static_cast<long long>(sizeof(T));
+    if (!RESIDUAL && sh.vector && !sh.wide && row_bytes >= kRmsRingMinRowBytes && n_rows * row_bytes >= kRingMinBytes) {
+        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, 1, true);
         if (rp.stages >= 2) {
             const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);
             int rc = LCE_OK;
-#define LCE_RMS_RING_FWD(VPT)                                                                                   \
-    rc = rms_ring_opt_in<rms_ring_forward_kernel<T, VPT, RESIDUAL>>(d);                                         \
-    if (rc == LCE_OK)                                                                                            \
-        rms_ring_forward_kernel<T, VPT, RESIDUAL><<<grid, sh.threads, rp.smem, s>>>(xp, rp_, wp, op, rop, rstd, n, h, \
-                                                                                    eps, rp.stages, d.status_ptr)
-            const T* rp_ = rp_src;
-            switch (sh.vpt) {
-                case 1: LCE_RMS_RING_FWD(1); break;
+#define LCE_RMS_RING_FWD(VPT)                                                                             \
+    rc = rms_ring_opt_in<rms_ring_forward_kernel<T, VPT>>(d);                                             \
+    if (rc == LCE_OK)                                                                                      \
+        rms_ring_forward_kernel<T, VPT><<<grid, sh.threads, rp.smem, s>>>(xp, wp, op, rstd, n, h, eps, rp.stages, \
+                                                                          d.status_ptr)
+            switch (sh.vpt) {  // rows of 8 KB and more never have one vector per thread
                 case 2: LCE_RMS_RING_FWD(2); break;
                 case 4: LCE_RMS_RING_FWD(4); break;
-                default: LCE_RMS_RING_FWD(8);
+                case 8: LCE_RMS_RING_FWD(8); break;
+                default: return LCE_ERR_ARG;
             }
 #undef LCE_RMS_RING_FWD
             if (rc != LCE_OK) return rc;

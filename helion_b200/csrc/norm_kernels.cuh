@@ -7,15 +7,17 @@
 //              dx = rstd * wd - (rstd^3 / H) * x * c   (+ dresidual)
 //              dweight = sum over rows of dy * x * rstd
 //
-// A CTA keeps one row in registers (VPT 16-byte vectors per thread), so every input element is read
-// from HBM exactly once and every output written once. Unlike the reference, whose backward reads dy
-// and x a second time to form dweight (tritium/ops/rmsnorm.py:383-439), the backward here is a single
-// pass: each thread owns the same columns for every row its CTA walks, accumulates their dweight
-// contributions in registers and writes one partial row per CTA at the end; rms_dw_reduce_kernel adds
-// the partial rows in a fixed order (no atomics: the same bits on every run).
+// Every input element is read from HBM exactly once and every output written once. Unlike the
+// reference, whose backward reads dy and x a second time to form dweight (tritium/ops/rmsnorm.py:383-439),
+// the backward here is a single pass: each thread owns the same columns for every row its CTA walks,
+// accumulates their dweight contributions in registers and writes one partial row per CTA at the end;
+// rms_dw_reduce_kernel adds the partial rows in a fixed order (no atomics: the same bits on every run).
 //
-// Rows too wide for the register-resident form (more than 256 threads x 8 vectors) take the
-// two-pass *_wide kernels; the second pass re-reads the row from L2.
+// Three forms, chosen by the host (lce_rmsnorm_forward / lce_rmsnorm_backward):
+//   ring      16-byte-aligned rows: rows stream into a shared-memory ring with cp.async.bulk (below);
+//   register  unaligned rows or odd widths (and small forwards): the CTA keeps ROWS rows packed in
+//             registers, element-wise loads where 16-byte ones are not legal;
+//   wide      rows beyond 256 threads x 8 vectors: two passes, the second one re-reads the row from L2.
 #pragma once
 
 #include "row_kernels.cuh"
@@ -305,14 +307,15 @@ __device__ __forceinline__ void rms_ring_drain(RmsRing& ring, int k_next, int st
     }
 }
 
-template <class T, int VPT, bool RESIDUAL>
+// Forward on the ring (plain rmsnorm; the residual form is faster on the register kernels).
+template <class T, int VPT>
 __global__ void __launch_bounds__(kRmsMaxThreads, 2)
-rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ weight,
-                        T* __restrict__ out, T* __restrict__ residual_out, float* __restrict__ rstd_out,
+rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ out,
+                        float* __restrict__ rstd_out,
                         int n_rows, int H, float eps, int stages, int* __restrict__ status) {
     const float inv_h = 1.0f / static_cast<float>(H);
     constexpr int VEC = RmsTile<T>::kVec;
-    constexpr int NS = RESIDUAL ? 2 : 1;
+    constexpr int NS = 1;
     constexpr int ROWS = RmsRingRows<VPT, NS>::kRows;
     constexpr bool kWeightUnpacked = VPT * VEC <= 16;  // else kept packed and unpacked per use
     extern __shared__ __align__(128) unsigned char ring_data[];
@@ -321,7 +324,7 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
     const int t = threadIdx.x;
     const long long n_groups = (static_cast<long long>(n_rows) + ROWS - 1) / ROWS;
     const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
-    const T* const srcs[2] = {x, residual};
+    const T* const srcs[1] = {x};
 
     if (t == 0) {
         for (int s = 0; s < stages; ++s) ptx::mbar_init(ptx::smem_u32(&ring.full[s]), 1);
@@ -359,13 +362,6 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
                     if (c < H) {
                         float z[VEC];
                         rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), z);
-                        if (RESIDUAL) {
-                            float q[VEC];
-                            rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), q);
-#pragma unroll
-                            for (int j = 0; j < VEC; ++j) z[j] += q[j];
-                            *reinterpret_cast<uint4*>(residual_out + (row0 + r) * H + c) = rms_pack<T>(z);
-                        }
 #pragma unroll
                         for (int j = 0; j < VEC; ++j) ss[r] = fmaf(z[j], z[j], ss[r]);
                     }
@@ -387,12 +383,6 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual,
                     if (c < H) {
                         float z[VEC], w[VEC];
                         rms_unpack<T>(*reinterpret_cast<const uint4*>(st + r * row_bytes + c * sizeof(T)), z);
-                        if (RESIDUAL) {
-                            float q[VEC];
-                            rms_unpack<T>(*reinterpret_cast<const uint4*>(st + (ROWS + r) * row_bytes + c * sizeof(T)), q);
-#pragma unroll
-                            for (int j = 0; j < VEC; ++j) z[j] += q[j];
-                        }
                         if (!kWeightUnpacked) rms_unpack<T>(wraw[i], w);
 #pragma unroll
                         for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * (kWeightUnpacked ? wf[i][j] : w[j]);
