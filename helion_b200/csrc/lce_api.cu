@@ -1273,7 +1273,7 @@ struct RmsShape {
     int rows;     // rows one CTA handles per step (RmsRows<vpt>)
 };
 
-RmsShape rms_shape(long long H, int dtype, bool all_aligned) {
+RmsShape rms_shape(long long H, int dtype, bool all_aligned, int n_streams = 1) {
     const long long vec = 16 / static_cast<long long>(elem_size(dtype));
     const int max_vpt = RmsTile<float>::kMaxVpt;
     RmsShape r;
@@ -1281,7 +1281,14 @@ RmsShape rms_shape(long long H, int dtype, bool all_aligned) {
     const long long nvec = cdiv(H, vec);
     r.wide = nvec > static_cast<long long>(max_vpt) * kRmsMaxThreads;
     r.vpt = 1;
-    while (r.vpt < max_vpt && cdiv(nvec, r.vpt) > 256) r.vpt *= 2;
+    static const int kThreadTarget = [] {  // HELION_B200_RMS_THREADS: threads per row aimed for (tuning knob)
+        const char* e = getenv("HELION_B200_RMS_THREADS");
+        return e && atoi(e) >= 32 && atoi(e) <= kRmsMaxThreads ? atoi(e) : kRmsMaxThreads;
+    }();
+    while (r.vpt < max_vpt && cdiv(nvec, r.vpt) > kThreadTarget) r.vpt *= 2;
+    // with two or three tensors streaming in, rows of 129..256 vectors measured 2-5 % faster on 128 threads
+    // with two vectors each than on 256 threads with one
+    if (n_streams >= 2 && r.vpt == 1 && nvec > 128) r.vpt = 2;
     const long long threads = cdiv(cdiv(nvec, r.vpt), 32) * 32;
     r.threads = r.wide ? kRmsMaxThreads : static_cast<int>(threads < 32 ? 32 : threads);
     r.rows = r.wide ? 1 : (r.vpt >= 4 ? 1 : 4 / r.vpt);
@@ -1541,7 +1548,7 @@ int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight,
     if (rc) return rc;
     const bool al = aligned16(x) && aligned16(weight) && aligned16(out) &&
                     (!residual || (aligned16(residual) && aligned16(residual_out)));
-    const RmsShape sh = rms_shape(hidden, dtype, al);
+    const RmsShape sh = rms_shape(hidden, dtype, al, residual ? 2 : 1);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define LCE_RMS_GO(T)                                                                                              \
     (residual ? rms_forward_launch<T, true>(*d, sh, x, residual, weight, out, residual_out, rstd, n_rows, hidden, \
@@ -1587,7 +1594,7 @@ int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, cons
     if (rc) return rc;
     const bool al = aligned16(dy) && aligned16(x) && aligned16(weight) && aligned16(dx) &&
                     (!dresidual || aligned16(dresidual));
-    const RmsShape sh = rms_shape(hidden, dtype, al);
+    const RmsShape sh = rms_shape(hidden, dtype, al, dresidual ? 3 : 2);
     switch (dtype) {
         case LCE_DTYPE_BF16:
             return rms_backward_launch<__nv_bfloat16>(*d, sh, dy, x, weight, rstd, dresidual, dx, dweight, n_rows, hidden,
