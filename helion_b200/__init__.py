@@ -6,6 +6,7 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 """
 
 from .ce_ops import cross_entropy, cross_entropy_backward
+from .decode_ops import greedy_head
 from .install import install, uninstall
 from .matmul_ops import matmul, matmul_vec
 from .norm_ops import residual_rmsnorm, rmsnorm, rmsnorm_backward
@@ -18,6 +19,7 @@ __all__ = [
     "cross_entropy",
     "cross_entropy_backward",
     "grad_sumsq",
+    "greedy_head",
     "install",
     "linear_cross_entropy",
     "linear_cross_entropy_backward",

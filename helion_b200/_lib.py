@@ -54,6 +54,8 @@ SIGNATURES = {
                                ctypes.c_float, ctypes.c_float, ctypes.c_float, c_int64, c_void_p, c_void_p]),
     "lce_sumsq_workspace_bytes": (c_size_t, []),
     "lce_sumsq": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "lce_greedy_head": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
     "lce_rmsnorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                     ctypes.c_float, c_int, c_void_p]),
     "lce_rmsnorm_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),

@@ -131,6 +131,67 @@ struct EpiStats {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Greedy decoding head: per (vocab tile, row) the maximum logit, sum exp(z - max) and the COLUMN of the
+// maximum (first one on ties), in the partial layout of EpiStats with the column's bits in the third
+// slot. Merged per row this gives argmax_v z[row, v] and its log-probability -log(sum exp(z - max))
+// without the logits ever reaching memory. No counterpart in the reference, whose decode step
+// materialises the logits through matmul (examples/common.py:127-131, 380-384).
+// ---------------------------------------------------------------------------------------------
+struct EpiTop1 {
+    struct Params {
+        int rows;   // valid rows
+        int vocab;  // valid columns (local shard width)
+        float* partial;
+        long long row_stride;
+    };
+    struct State {
+        float m, s;
+        int arg;  // local column of the running maximum
+        int row;
+    };
+    static __device__ __forceinline__ void begin(State& st, const Params&, const TileCtx& tc) {
+        st.row = tc.m_tile * kBM + tc.row_in_tile;
+        st.m = -INFINITY;
+        st.s = 0.f;
+        st.arg = tc.n_tile * tc.bn;
+    }
+    static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
+                                                 int col0, float (&v)[32]) {
+        const int gcol0 = tc.n_tile * tc.bn + col0;
+        if (gcol0 >= p.vocab) return;
+        if (gcol0 + 32 > p.vocab) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (gcol0 + j >= p.vocab) v[j] = -INFINITY;
+        }
+        float cm = v[0];
+        int cj = 0;
+#pragma unroll
+        for (int j = 1; j < 32; ++j)
+            if (v[j] > cm) {  // strict: the first maximum wins
+                cm = v[j];
+                cj = j;
+            }
+        if (cm > st.m) st.arg = gcol0 + cj;  // chunks arrive in ascending column order
+        const float nm = fmaxf(st.m, cm);
+        const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += ptx::ex2(fmaf(v[j], kLog2e, -nm2));
+        st.s = st.s * ptx::ex2(fmaf(st.m, kLog2e, -nm2)) + acc;
+        st.m = nm;
+    }
+    static __device__ __forceinline__ void end(State& st, const Params& p, const TileCtx& tc) {
+        if (st.row < p.rows) {
+            float* base = p.partial + static_cast<long long>(tc.n_tile) * 3 * p.row_stride + st.row;
+            base[0] = st.m;
+            base[p.row_stride] = st.s;
+            base[2 * p.row_stride] = __int_as_float(st.arg);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
 // Backward step 1: recompute a logits tile and turn it into the logit gradient
 //   G[row, col] = (exp(z - lse[row]) - [col == target[row]]) * rowscale[row]
 // rounded to the input dtype (the reference rounds G the same way before its two GEMMs,

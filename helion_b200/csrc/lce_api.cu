@@ -345,6 +345,37 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
+// Greedy head: the forward GEMM with the argmax epilogue, then the per-row merge.
+template <class T>
+int greedy_head_impl(const DeviceInfo& d, bool use_tc, const void* x, const void* w, long long N, long long H,
+                     long long V, long long vocab_start, long long* token, float* logprob, float* lse, void* ws,
+                     cudaStream_t stream) {
+    const FwdLayout l = fwd_layout(N, V, use_tc);
+    EpiTop1::Params ep;
+    ep.rows = static_cast<int>(N);
+    ep.vocab = static_cast<int>(V);
+    ep.partial = static_cast<float*>(ws);
+    ep.row_stride = l.row_stride;
+    const Mat a{x, N, H, H}, b{w, V, H, H};
+    int rc;
+    if (use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+            rc = launch_tc<false, false, kBf16, EpiTop1>(d, a, b, N, V, H, 1, ep, stream);
+        } else {
+            rc = LCE_ERR_ARG;
+        }
+    } else {
+        rc = launch_simt<T, EpiTop1>(d, a, false, b, false, N, V, H, ep, stream);
+    }
+    if (rc) return rc;
+    merge_top1_kernel<<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, stream>>>(
+        static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), vocab_start,
+        token, logprob, lse);
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
 // ---------------------------------------------------------------------------------------------
 // backward block plan
 // ---------------------------------------------------------------------------------------------
@@ -639,6 +670,30 @@ int lce_forward_stats(const void* x, const void* w, const void* target, int targ
             return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         default:
             return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+    }
+}
+
+int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
+                    int64_t* token, float* logprob, float* lse, void* ws, size_t ws_bytes, unsigned flags,
+                    void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (N == 0) return LCE_OK;
+    if (!x || !w || !token || !logprob || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    if (ws_bytes < fwd_layout(N, V, use_tc).bytes) return LCE_ERR_WS_TOO_SMALL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long* tok = reinterpret_cast<long long*>(token);
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            return greedy_head_impl<__nv_bfloat16>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+        case LCE_DTYPE_F16:
+            return greedy_head_impl<__half>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+        default:
+            return greedy_head_impl<float>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
     }
 }
 

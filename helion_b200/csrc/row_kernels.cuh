@@ -62,6 +62,42 @@ merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long 
     }
 }
 
+// Greedy head: partial [n_tiles][3][row_stride] of EpiTop1 -> token[N] (global vocabulary index of the
+// largest logit; the lowest index on ties), logprob[N] = log softmax at that token, optionally lse[N].
+// Same CTA shape and fold order as merge_partials_kernel.
+__device__ __forceinline__ void merge_top1(float& m, float& s, int& a, float bm, float bs, int ba) {
+    if (bm > m || (bm == m && ba < a)) a = ba;
+    merge_ms(m, s, bm, bs);
+}
+
+__global__ void __launch_bounds__(kMergeRows * kMergeLanes)
+merge_top1_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N, long long vocab_start,
+                  long long* __restrict__ token, float* __restrict__ logprob, float* __restrict__ lse) {
+    __shared__ float sm[kMergeLanes][kMergeRows + 1], ss[kMergeLanes][kMergeRows + 1];
+    __shared__ int sa[kMergeLanes][kMergeRows + 1];
+    const int r = threadIdx.x % kMergeRows, j = threadIdx.x / kMergeRows;
+    const int row = blockIdx.x * kMergeRows + r;
+    float m = -INFINITY, s = 0.f;
+    int a = 0x7fffffff;
+    if (row < N) {
+        for (int b = j; b < n_tiles; b += kMergeLanes) {
+            const float* base = partial + static_cast<long long>(b) * 3 * row_stride + row;
+            merge_top1(m, s, a, base[0], base[row_stride], __float_as_int(base[2 * row_stride]));
+        }
+    }
+    sm[j][r] = m;
+    ss[j][r] = s;
+    sa[j][r] = a;
+    __syncthreads();
+    if (j == 0 && row < N) {
+        for (int k = 1; k < kMergeLanes; ++k) merge_top1(m, s, a, sm[k][r], ss[k][r], sa[k][r]);
+        const float log_s = logf(s);
+        token[row] = vocab_start + a;
+        logprob[row] = -log_s;
+        if (lse != nullptr) lse[row] = m + log_s;
+    }
+}
+
 // stats: [R][3][N] -> lse[N], per-row loss (0 for ignored rows).
 // A target outside the vocabulary that is not ignore_index leaves target_logit = -inf and the
 // row loss +inf, as in the reference (tritium/ops/cross_entropy.py:240-244, 286-287).

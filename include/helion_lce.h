@@ -222,6 +222,16 @@ size_t lce_sumsq_workspace_bytes(void);
 int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, void* ws, size_t ws_bytes,
               void* stream);
 
+/* ---- greedy decoding head ----------------------------------------------------------------------------
+ * token[row] = vocab_start + argmax_v (x[row] . w[v]) (the lowest index on ties), logprob[row] = log softmax of
+ * the row at that token, lse[row] (NULL: not written) = the row's logsumexp - the logits are never materialised.
+ * Replaces, for greedy sampling, the logits product of the reference's decode step
+ * (examples/common.py:127-131, :380-384: tritium.matmul / matmul_vec on lm_head.T.contiguous(), a V x H
+ * transpose copy and an N x V write per step). ws: lce_forward_workspace_bytes(N, H, V, dtype, flags). */
+int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
+                    int64_t* token, float* logprob, float* lse, void* ws, size_t ws_bytes, unsigned flags,
+                    void* stream);
+
 /* ---- producer of the hidden states -----------------------------------------------------------------
  * lce_rmsnorm_forward replaces the launches of tritium.rmsnorm and tritium.residual_rmsnorm
  * (tritium/ops/rmsnorm.py:29-84, :325-349, :749-778) on [n_rows, hidden] row-major tensors of `dtype`:

@@ -249,6 +249,22 @@ def restated_adamw_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.
 
 
 # ----------------------------------------------------------------------------------------------
+# greedy decoding head
+# ----------------------------------------------------------------------------------------------
+def greedy_expression(hidden: torch.Tensor, weight: torch.Tensor) -> dict:
+    """What the reference's decode step computes before sampling (examples/common.py:127-131: logits =
+    hidden @ lm_head.T), reduced the greedy way: fp32 logits of the dtype-rounded inputs, their argmax
+    (first index on ties, as torch.argmax), log_softmax at it, and the logsumexp."""
+    z = hidden.detach().float().reshape(-1, hidden.shape[-1]) @ weight.detach().float().T
+    lse = torch.logsumexp(z, dim=-1)
+    token = z.argmax(dim=-1)
+    top = z.gather(1, token[:, None])[:, 0]
+    shape = hidden.shape[:-1]
+    return {"token": token.reshape(shape), "logprob": (top - lse).reshape(shape), "lse": lse.reshape(shape),
+            "logits": z}
+
+
+# ----------------------------------------------------------------------------------------------
 # producer of the hidden states: RMSNorm / residual RMSNorm
 # ----------------------------------------------------------------------------------------------
 def restated_rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,

@@ -285,3 +285,21 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["higher_is_better"] is True
     assert line["config"]["workload"] == "smoke"
+
+
+def test_greedy_head_rejects_cpu_tensors_before_touching_the_library():
+    from helion_b200 import decode_ops
+
+    with pytest.raises(ValueError, match="hidden must be a CUDA tensor"):
+        decode_ops.greedy_head(torch.randn(2, 8), torch.randn(16, 8))
+
+
+def test_oracle_greedy_expression_is_argmax_of_log_softmax():
+    from oracle import oracle
+
+    g = torch.Generator().manual_seed(3)
+    h, w = torch.randn(2, 5, 16, generator=g).bfloat16(), torch.randn(40, 16, generator=g).bfloat16()
+    e = oracle.greedy_expression(h, w)
+    ls = torch.log_softmax(h.float().reshape(-1, 16) @ w.float().T, dim=-1)
+    assert torch.equal(e["token"].reshape(-1), ls.argmax(dim=-1))
+    torch.testing.assert_close(e["logprob"].reshape(-1), ls.max(dim=-1).values, rtol=1e-6, atol=1e-6)
