@@ -7,21 +7,25 @@ row's logsumexp is needed, and those are what the forward of the fused linear-cr
 reduces to per vocabulary tile: this op runs that forward with an argmax epilogue. It takes the LM-head
 weight as it is stored (``[V, H]``) and returns ``(token, logprob)`` shaped like ``hidden.shape[:-1]``.
 No counterpart in the reference (new entry point; ``install()`` does not rebind anything to it).
+
+With ``process_group`` the weight is this rank's contiguous vocabulary shard (as for the fused loss): every
+rank reduces its shard, one all-gather of 16 bytes per row follows, and all ranks merge to the same result.
 """
 
 from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, parallel
 from .ops import FLOAT_DTYPES, _DTYPE_CODE, _need_contiguous, _need_cuda, _need_dtype, _on_device, _path_flags, _stream, \
     _workspace
 
 
-def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int = 0,
-                return_logsumexp: bool = False):
+def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int | None = None,
+                return_logsumexp: bool = False, process_group=None):
     """``(token, logprob)`` - int64 index of the largest logit of every row (lowest index on ties, offset by
-    ``vocab_start``) and float32 ``log_softmax`` at it; with ``return_logsumexp`` also the row's logsumexp."""
+    ``vocab_start``) and float32 ``log_softmax`` at it; with ``return_logsumexp`` also the row's logsumexp.
+    ``vocab_start`` defaults to 0, or to ``rank * weight.shape[0]`` when a ``process_group`` is given."""
     _need_cuda("hidden", hidden)
     _need_cuda("weight", weight)
     _need_dtype("hidden", hidden, FLOAT_DTYPES)
@@ -46,9 +50,12 @@ def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int 
     shape = tuple(hidden.shape[:-1])
     n_rows = hidden.numel() // hidden_size
     dev = hidden.device
+    rank, world = parallel.group_rank_size(process_group)
+    if vocab_start is None:
+        vocab_start = rank * vocab_size
     token = torch.empty(shape, dtype=torch.int64, device=dev)
     logprob = torch.empty(shape, dtype=torch.float32, device=dev)
-    lse = torch.empty(shape, dtype=torch.float32, device=dev) if return_logsumexp else None
+    lse = torch.empty(shape, dtype=torch.float32, device=dev) if return_logsumexp or world > 1 else None
     if n_rows:
         L = _lib.lib()
         flags = _path_flags()
@@ -61,4 +68,7 @@ def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int 
                                   ws.data_ptr(), ws.numel(), flags, _stream(dev)),
                 "lce_greedy_head",
             )
+    if world > 1:
+        merged = parallel.merge_greedy(parallel.gather_stats(parallel.pack_greedy(token, logprob, lse), process_group))
+        token, logprob, lse = (t.reshape(shape) for t in merged)
     return (token, logprob, lse) if return_logsumexp else (token, logprob)

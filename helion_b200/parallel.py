@@ -54,6 +54,29 @@ def gather_stats(stats: torch.Tensor, process_group: Any) -> torch.Tensor:
     return out
 
 
+def pack_greedy(token: torch.Tensor, logprob: torch.Tensor, lse: torch.Tensor) -> torch.Tensor:
+    """One shard's greedy result as ``[4, N]`` float32: (largest logit, logsumexp, the int64 token's two
+    32-bit halves) - a single buffer, so that one all-gather carries everything."""
+    n = token.numel()
+    buf = torch.empty((4, n), dtype=torch.float32, device=token.device)
+    buf[0] = logprob.reshape(-1) + lse.reshape(-1)
+    buf[1] = lse.reshape(-1)
+    buf[2:4].reshape(-1).view(torch.int64).copy_(token.reshape(-1))
+    return buf
+
+
+def merge_greedy(gathered: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``[R, 4, N]`` packed shard results (rank order) -> (token, logprob, logsumexp) of the whole vocabulary.
+    The row's logsumexp is the logsumexp of the shards'; the token comes from the shard with the largest
+    logit, the lowest rank - i.e. the lowest index for contiguous ascending shards - on ties."""
+    world, _, n = gathered.shape
+    tops, lses = gathered[:, 0], gathered[:, 1]
+    tokens = gathered[:, 2:4].reshape(world, 2 * n).contiguous().view(torch.int64)
+    lse = torch.logsumexp(lses, dim=0)
+    best = tops.argmax(dim=0, keepdim=True)
+    return tokens.gather(0, best)[0], tops.gather(0, best)[0] - lse, lse
+
+
 def reduce_dx(dx_partial: torch.Tensor, out_dtype: torch.dtype, process_group: Any) -> torch.Tensor:
     """Sum the fp32 partial ``dX`` of all ranks and round to ``out_dtype`` once."""
     rank, world = group_rank_size(process_group)

@@ -65,6 +65,13 @@ def _worker(rank: int, world: int, port: int, results, dx_reduce: str = "p2p") -
             both = [torch.empty_like(loss) for _ in range(world)]
             dist.all_gather(both, loss)
             assert all(torch.equal(both[0], b) for b in both)
+        # greedy head over the sharded vocabulary = greedy head over the whole one
+        from helion_b200 import decode_ops
+
+        tok_full, lp_full = decode_ops.greedy_head(x.detach(), w_full.detach())
+        tok, lp = decode_ops.greedy_head(xs.detach(), w_loc.detach(), process_group=dist.group.WORLD)
+        assert torch.equal(tok, tok_full)
+        torch.testing.assert_close(lp, lp_full, rtol=1e-5, atol=1e-5)
         assert _lib.device_status() == 0
         dist.barrier()
         dist.destroy_process_group()

@@ -66,6 +66,14 @@ def _worker(rank: int, world: int, port: int, scenario: str, results) -> None:
         assert dx.dtype == torch.bfloat16
         err = (dx.float() - full["dx"]).abs().max() / full["dx"].abs().max()
         assert err < 1e-2, float(err)
+        # greedy head: each rank reduces its shard, one all-gather, every rank merges to the unsharded answer
+        local = oracle.greedy_expression(x, w_loc)
+        packed = parallel.pack_greedy(local["token"] + start, local["logprob"], local["lse"])
+        token, logprob, lse = parallel.merge_greedy(parallel.gather_stats(packed, dist.group.WORLD))
+        whole = oracle.greedy_expression(x, w)
+        assert torch.equal(token, whole["token"])
+        torch.testing.assert_close(logprob, whole["logprob"], rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(lse, whole["lse"], rtol=1e-5, atol=1e-5)
         # every rank ends with identical bits
         gathered = [torch.empty_like(merged["lse"]) for _ in range(world)]
         dist.all_gather(gathered, merged["lse"])
@@ -101,3 +109,29 @@ def test_missing_rank_becomes_an_error_not_a_hang():
     res = _run("rank1_never_joins")
     assert res[1] == "left"
     assert res[0].startswith("error"), res
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_greedy_merge_over_shards_is_the_unsharded_argmax(world):
+    """The merge alone (no process group): tokens beyond 2^31 survive the float32 packing, and a maximum
+    that appears in two shards resolves to the lower index."""
+    from helion_b200 import parallel
+    from oracle import oracle
+
+    g = torch.Generator().manual_seed(world)
+    x = torch.randn(33, 24, generator=g).bfloat16()
+    w = (torch.randn(8 * 125, 24, generator=g) * 0.3).bfloat16()
+    w[900] = w[17] = x[0] * 3  # the same winning row in the first and in the last shard
+    packed = []
+    for r in range(world):
+        s, e = parallel.shard_bounds(w.shape[0], world, r)
+        loc = oracle.greedy_expression(x, w[s:e])
+        packed.append(parallel.pack_greedy(loc["token"] + s, loc["logprob"], loc["lse"]))
+    token, logprob, lse = parallel.merge_greedy(torch.stack(packed))
+    whole = oracle.greedy_expression(x, w)
+    assert torch.equal(token, whole["token"]) and int(token[0]) == 17
+    torch.testing.assert_close(logprob, whole["logprob"], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(lse, whole["lse"], rtol=1e-5, atol=1e-5)
+    big = torch.tensor([5_000_000_123, 7], dtype=torch.int64)
+    buf = parallel.pack_greedy(big, torch.zeros(2), torch.zeros(2))
+    assert torch.equal(parallel.merge_greedy(buf[None])[0], big)
