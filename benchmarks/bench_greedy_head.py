@@ -7,7 +7,7 @@ bandwidth. Providers: ``helion_b200`` (``greedy_head``: argmax and log-probabili
 ``matmul(hidden, lm_head.T.contiguous())`` - the transpose copy included - then argmax; torch.matmul stands in
 for tritium.matmul so that only the extra copy and the logits write are being compared).
 
-    python -m benchmarks.bench_greedy_head [--rows 1,16,128,1024]
+    python -m benchmarks.bench_greedy_head [--rows 1,16,128,1024] [--providers helion_b200,...]
 """
 
 from __future__ import annotations
@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--rows", default="1,16,128,1024")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--providers", default="helion_b200,torch_eager,reference_decode")
     args = ap.parse_args()
     require_cuda()
     peaks = ROOT / "MEASURED_PEAKS.json"
@@ -47,6 +48,8 @@ def main() -> None:
 
         for provider, fn in (("helion_b200", lambda: helion_b200.greedy_head(hidden, weight)),
                              ("torch_eager", eager), ("reference_decode", lambda: (hidden @ weight.T.contiguous()).argmax(dim=-1))):  # the transpose copy per step
+            if provider not in args.providers.split(","):
+                continue
             ms = bench_ms(fn)
             print(json.dumps({"rows": n, "hidden": h, "vocab": v, "provider": provider, "ms": ms,
                               "weight_gbs": wbytes / (ms * 1e-3) / 1e9, "frac_of_hbm": wbytes / (ms * 1e-3) / 1e9 / hbm}),
