@@ -59,6 +59,7 @@ SIGNATURES = {
     "lce_rmsnorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                     ctypes.c_float, c_int, c_void_p]),
     "lce_rmsnorm_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "lce_rmsnorm_plan": (c_int, [c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "lce_rmsnorm_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, ctypes.c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,

@@ -1415,6 +1415,29 @@ int rms_ring_grid(const DeviceInfo& d, const RmsShape& sh, const RmsRingPlan& rp
     return static_cast<int>(groups < g ? groups : g);
 }
 
+// Which form a forward / backward takes (the launch code and lce_rmsnorm_plan both ask here).
+// Forward: plain rmsnorm of rows of 8 KB and more streams through the shared-memory ring once the input
+// reaches kRmsRingMinBytes; narrower rows, small inputs and the residual form are faster on the register
+// kernels (measured: the ring's set-up costs ~2 us, and with two tensors streaming in it gains nothing).
+bool rms_forward_uses_ring(const RmsShape& sh, long long n_rows, long long H, int dtype, bool residual, RmsRingPlan* rp) {
+    static const long long kRingMinBytes = [] {  // HELION_B200_RMS_RING_MIN_MB overrides (tuning knob)
+        const char* e = getenv("HELION_B200_RMS_RING_MIN_MB");
+        return e ? atoll(e) << 20 : kRmsRingMinBytes;
+    }();
+    const long long row_bytes = H * static_cast<long long>(elem_size(dtype));
+    if (residual || !sh.vector || sh.wide || row_bytes < kRmsRingMinRowBytes || n_rows * row_bytes < kRingMinBytes)
+        return false;
+    *rp = rms_ring_plan(sh, H, dtype, 1, true);
+    return rp->stages >= 2;
+}
+
+// Backward: the ring whenever 16-byte copies are legal and two stages fit.
+bool rms_backward_uses_ring(const RmsShape& sh, long long H, int dtype, bool has_dres, RmsRingPlan* rp) {
+    if (!sh.vector || sh.wide) return false;
+    *rp = rms_ring_plan(sh, H, dtype, has_dres ? 3 : 2, false);
+    return rp->stages >= 2;
+}
+
 template <class T, bool RESIDUAL>
 int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, const void* residual,
                        const void* weight, void* out, void* residual_out, float* rstd, long long n_rows,
@@ -1425,17 +1448,9 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     T* op = static_cast<T*>(out);
     T* rop = static_cast<T*>(residual_out);
     const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
-    // Plain rmsnorm of rows of 8 KB and more streams through the shared-memory ring once the input reaches
-    // kRmsRingMinBytes; narrower rows, small inputs and the residual form are faster on the register kernels
-    // (measured: the ring's set-up costs ~2 us, and with two tensors streaming in it gains nothing).
-    static const long long kRingMinBytes = [] {  // HELION_B200_RMS_RING_MIN_MB overrides (tuning knob)
-        const char* e = getenv("HELION_B200_RMS_RING_MIN_MB");
-        return e ? atoll(e) << 20 : kRmsRingMinBytes;
-    }();
-    const long long row_bytes = H * static_cast<long long>(sizeof(T));
-    if (!RESIDUAL && sh.vector && !sh.wide && row_bytes >= kRmsRingMinRowBytes && n_rows * row_bytes >= kRingMinBytes) {
-        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, 1, true);
-        if (rp.stages >= 2) {
+    {
+        RmsRingPlan rp;
+        if (rms_forward_uses_ring(sh, n_rows, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL, &rp)) {
             const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);
             int rc = LCE_OK;
 #define LCE_RMS_RING_FWD(VPT)                                                                             \
@@ -1517,8 +1532,7 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
             LCE_COUNT_LAUNCH();
             if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
         }
-    } else if (sh.vector && rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2, false).stages >= 2) {
-        const RmsRingPlan rp = rms_ring_plan(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp ? 3 : 2, false);
+    } else if (RmsRingPlan rp; rms_backward_uses_ring(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp != nullptr, &rp)) {
         const int grid = rms_ring_grid(d, sh, rp, n_rows, kRmsMaxPartials);
         n_partials = grid;
         int rc = LCE_OK;
@@ -1615,6 +1629,31 @@ int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight,
         default: return LCE_RMS_GO(float);
     }
 #undef LCE_RMS_GO
+}
+
+int lce_rmsnorm_plan(int64_t n_rows, int64_t hidden, int dtype, int op, int aligned, int sm_count, int64_t* out) {
+    using namespace lce;
+    if (!out || n_rows < 1 || hidden < 1 || hidden > 0x7fffffffll / 16 || op < 0 || op > 3 || sm_count < 1) return LCE_ERR_ARG;
+    if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
+    const bool forward = op < 2;
+    const int n_streams = op == 0 ? 1 : op == 1 ? 2 : op;
+    const RmsShape sh = rms_shape(hidden, dtype, aligned != 0, n_streams);
+    DeviceInfo d;
+    d.sm_count = sm_count;
+    RmsRingPlan rp{};
+    const bool ring = forward ? rms_forward_uses_ring(sh, n_rows, hidden, dtype, op == 1, &rp)
+                              : rms_backward_uses_ring(sh, hidden, dtype, op == 3, &rp);
+    out[0] = ring ? 0 : sh.wide ? 2 : 1;
+    out[1] = sh.vpt;
+    out[2] = sh.threads;
+    out[3] = ring ? rp.rows : sh.rows;
+    out[4] = ring ? rp.ctas_per_sm : 0;
+    out[5] = ring ? rp.stages : 0;
+    out[6] = ring ? static_cast<int64_t>(rp.smem) : 0;
+    const long long cap = forward ? 0 : kRmsMaxPartials;
+    out[7] = ring ? rms_ring_grid(d, sh, rp, n_rows, cap)
+                  : rms_grid(d, sh.wide ? n_rows : cdiv(n_rows, sh.rows), sh.threads, sh.wide && !forward ? 0 : cap);
+    return LCE_OK;
 }
 
 size_t lce_rmsnorm_backward_workspace_bytes(int64_t n_rows, int64_t hidden, int dtype) {

@@ -249,6 +249,13 @@ int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t 
 int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
                         float* rstd, int64_t n_rows, int64_t hidden, float eps, int dtype, void* stream);
 size_t lce_rmsnorm_backward_workspace_bytes(int64_t n_rows, int64_t hidden, int dtype);
+/* How a call would run (host arithmetic only; no device needed): op 0 rmsnorm forward, 1 residual forward,
+ * 2 backward, 3 backward with dresidual; aligned = all pointers 16-byte aligned. out[0] form (0 shared-memory
+ * ring, 1 register-resident rows, 2 two-pass wide rows), out[1] 16-byte vectors per thread, out[2] threads per
+ * CTA, out[3] rows per step, out[4] CTAs per SM / out[5] stages / out[6] dynamic shared memory bytes of the
+ * ring (0 otherwise), out[7] CTAs launched on a device of sm_count SMs. The counterpart of the reference's
+ * block-size and staged-dweight heuristics (tritium/ops/rmsnorm.py:338, :371-380). */
+int lce_rmsnorm_plan(int64_t n_rows, int64_t hidden, int dtype, int op, int aligned, int sm_count, int64_t* out);
 int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, const float* rstd,
                          const void* dresidual, void* dx, void* dweight, int64_t n_rows, int64_t hidden, float eps,
                          int dtype, void* ws, size_t ws_bytes, void* stream);

@@ -102,3 +102,70 @@ def test_cpu_tensors_are_rejected_like_the_reference():
 
 def test_next_pow2_limit():
     assert norm_ops._next_pow2(1) == 1 and norm_ops._next_pow2(65536) == 65536 and norm_ops._next_pow2(65537) == 131072
+
+
+# ---- the launch plan (host arithmetic of the library; no device needed) ------------------------------
+import ctypes  # noqa: E402
+
+from helion_b200 import _lib  # noqa: E402
+
+RING, REGISTER, WIDE = 0, 1, 2
+ELEM = {_lib.DTYPE_BF16: 2, _lib.DTYPE_F16: 2, _lib.DTYPE_F32: 4}
+
+
+def _plan(n_rows, hidden, dtype, op, aligned=1, sm_count=148):
+    out = (ctypes.c_int64 * 8)()
+    assert _lib.lib().lce_rmsnorm_plan(n_rows, hidden, dtype, op, aligned, sm_count, out) == 0
+    return dict(zip(("form", "vpt", "threads", "rows", "ctas", "stages", "smem", "grid"), out))
+
+
+@pytest.mark.parametrize("dtype", [_lib.DTYPE_BF16, _lib.DTYPE_F32])
+@pytest.mark.parametrize("op", [0, 1, 2, 3])
+def test_launch_plan_invariants(dtype, op):
+    """For every width the reference's tests use and a sweep around the form boundaries: the threads of a
+    CTA cover the row, the ring fits the shared memory of an SM with at least two stages, the backward never
+    launches more CTAs than it has partial dweight rows, and the workspace covers them."""
+    L = _lib.lib()
+    vec = 16 // ELEM[dtype]
+    n_streams = (1, 2, 2, 3)[op]
+    widths = [8, 64, 100, 256, 520, 1024, 1536, 2048, 2560, 3072, 3584, 4096, 5120, 6144, 8192, 11008, 16384, 16392,
+              32768, 65536]
+    for hidden in widths:
+        for n_rows in (1, 7, 128, 4097, 16384, 1 << 20):
+            p = _plan(n_rows, hidden, dtype, op)
+            nvec = -(-hidden // vec)
+            assert p["threads"] % 32 == 0 and 32 <= p["threads"] <= 256
+            assert 1 <= p["grid"] <= n_rows
+            if p["form"] == WIDE:
+                assert nvec > 8 * 256
+                continue
+            assert p["vpt"] in (1, 2, 4, 8) and p["vpt"] * p["threads"] >= nvec and p["rows"] in (1, 2, 4, 8)
+            if p["form"] == RING:
+                assert hidden % vec == 0 and 2 <= p["stages"] <= 4 and 2 <= p["ctas"] <= 8
+                assert p["smem"] == p["stages"] * p["rows"] * n_streams * hidden * ELEM[dtype] <= 100 * 1024
+                assert p["ctas"] * (p["smem"] + 3 * 1024) <= 228 * 1024  # what an SM has, static and reserved included
+                assert p["grid"] <= 148 * p["ctas"]
+            if op >= 2:
+                assert p["grid"] <= 592
+                ws = L.lce_rmsnorm_backward_workspace_bytes(n_rows, hidden, dtype)
+                assert ws >= p["grid"] * hidden * 4 + n_rows * 4
+
+
+def test_launch_plan_forms():
+    bf16 = _lib.DTYPE_BF16
+    # plain forward: the ring from 8 KB rows and 16 MiB of input, registers below; the residual form never
+    assert _plan(16384, 4096, bf16, 0)["form"] == RING and _plan(16384, 2048, bf16, 0)["form"] == REGISTER
+    assert _plan(1024, 4096, bf16, 0)["form"] == REGISTER and _plan(16384, 4096, bf16, 1)["form"] == REGISTER
+    # backward: the ring whenever 16-byte copies are legal
+    assert _plan(1, 1024, bf16, 2)["form"] == RING and _plan(16384, 4096, bf16, 3)["form"] == RING
+    assert _plan(16, 100, bf16, 2)["form"] == REGISTER and _plan(16, 1024, bf16, 2, aligned=0)["form"] == REGISTER
+    # rows beyond 256 threads x 8 vectors
+    assert _plan(4, 16392, bf16, 0)["form"] == WIDE and _plan(4, 11008, _lib.DTYPE_F32, 2)["form"] == WIDE
+    # Llama-3 width: 256 threads x 2 vectors; 4 KB rows with several tensors streaming in: 128 x 2
+    p = _plan(16384, 4096, bf16, 2)
+    assert (p["vpt"], p["threads"], p["rows"], p["ctas"], p["stages"]) == (2, 256, 2, 2, 3)
+    assert (_plan(32768, 2048, bf16, 2)["vpt"], _plan(32768, 2048, bf16, 2)["threads"]) == (2, 128)
+    assert (_plan(32768, 2048, bf16, 0)["vpt"], _plan(32768, 2048, bf16, 0)["threads"]) == (1, 256)
+    out = (ctypes.c_int64 * 8)()
+    assert _lib.lib().lce_rmsnorm_plan(0, 1024, bf16, 0, 1, 148, out) == 1  # invalid argument
+    assert _lib.lib().lce_rmsnorm_plan(4, 1024, 9, 0, 1, 148, out) == 1
