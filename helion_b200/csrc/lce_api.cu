@@ -1607,7 +1607,8 @@ extern "C" {
 int lce_rmsnorm_forward(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
                         float* rstd, int64_t n_rows, int64_t hidden, float eps, int dtype, void* stream) {
     using namespace lce;
-    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fffffffll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
+    // row indices are ints in the kernels, and a CTA steps past the end by up to grid x rows-per-step before it stops
+    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fff0000ll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
     if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
     if ((residual == nullptr) != (residual_out == nullptr)) return LCE_ERR_ARG;
     if (n_rows == 0) return LCE_OK;
@@ -1666,7 +1667,8 @@ int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, cons
                          void* dx, void* dweight, int64_t n_rows, int64_t hidden, float eps, int dtype, void* ws,
                          size_t ws_bytes, void* stream) {
     using namespace lce;
-    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fffffffll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
+    // row indices are ints in the kernels, and a CTA steps past the end by up to grid x rows-per-step before it stops
+    if (n_rows < 0 || hidden < 1 || n_rows > 0x7fff0000ll || hidden > 0x7fffffffll / 16) return LCE_ERR_ARG;
     if (dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_F32) return LCE_ERR_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (n_rows == 0) {  // dweight of an empty batch is zero
