@@ -40,6 +40,7 @@ SIGNATURES = {
                              c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
                              c_uint, c_size_t, c_void_p, c_void_p, c_void_p]),
     "lce_dx_reduce_gather": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "lce_dx_reduce_slice": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "lce_backward_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t, c_void_p, c_void_p,
                                   ctypes.POINTER(c_int64)]),
     "lce_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),

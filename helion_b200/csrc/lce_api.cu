@@ -37,8 +37,6 @@ struct DeviceInfo {
     int* status_ptr = nullptr;
 };
 
-// Which tcgen05 variant the GEMM launches use; set per call from the flags.
-thread_local int t_cta_group = 2;
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mutex;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -82,9 +80,40 @@ inline size_t elem_size(int dtype) { return dtype == LCE_DTYPE_F32 ? 4 : 2; }
 
 // 2-D tensor map over a row-major 16-bit matrix: `inner` contiguous elements per row, `outer`
 // rows, `pitch_bytes` between rows; 128-byte swizzle; out-of-range elements read as zero.
+// Encoding is host-only work (no driver state is touched), but it costs about a microsecond per map and
+// a training step issues the same handful of maps over and over, so finished maps are kept in a small
+// per-thread, direct-mapped cache keyed by everything the encoding depends on.
+struct TmapKey {
+    const void* base;
+    long long inner, outer, pitch_bytes;
+    unsigned box_inner, box_outer;
+    int dtype;
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && pitch_bytes == o.pitch_bytes &&
+               box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype;
+    }
+};
+struct TmapSlot {
+    TmapKey key;
+    bool valid = false;
+    CUtensorMap map;
+};
+constexpr int kTmapCacheSlots = 64;
+
 int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, long long outer,
               long long pitch_bytes, unsigned box_inner, unsigned box_outer) {
     if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_bytes & 15) != 0) return LCE_ERR_ALIGN;
+    static thread_local TmapSlot cache[kTmapCacheSlots];
+    const TmapKey key{base, inner, outer, pitch_bytes, box_inner, box_outer, dtype};
+    unsigned long long h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h = h * 0x9E3779B97F4A7C15ull ^ static_cast<unsigned long long>(inner) * 0xC2B2AE3D27D4EB4Full ^
+        static_cast<unsigned long long>(outer) * 0x165667B19E3779F9ull ^ (static_cast<unsigned long long>(box_outer) << 7) ^
+        static_cast<unsigned long long>(pitch_bytes);
+    TmapSlot& slot = cache[(h ^ (h >> 29)) % kTmapCacheSlots];
+    if (slot.valid && slot.key == key) {
+        *tm = slot.map;
+        return LCE_OK;
+    }
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
     cuuint32_t box[2] = {box_inner, box_outer};
@@ -94,7 +123,11 @@ int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, lon
     const CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LCE_OK : LCE_ERR_CUDA;
+    if (r != CUDA_SUCCESS) return LCE_ERR_CUDA;
+    slot.key = key;
+    slot.map = *tm;
+    slot.valid = true;
+    return LCE_OK;
 }
 
 // One operand of a GEMM as the host sees it: a row-major matrix [rows, cols] with a pitch.
@@ -136,11 +169,12 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     if (k_splits < 1 || (k_splits - 1) * cdiv(k_blocks, k_splits) >= k_blocks) return LCE_ERR_ARG;
     auto kern = gemm_tc_kernel<kBN, kStages, CG, A_MN, B_MN, IS_BF16, Epi>;
     constexpr int smem = GemmSmem<kBN, kStages, CG>::kTotalBytes;
-    static bool smem_opted_in[kMaxDevices] = {};  // per kernel instantiation and device
-    if (!smem_opted_in[d.index]) {
+    // per kernel instantiation and device; setting the attribute twice from two threads is harmless
+    static std::atomic<bool> smem_opted_in[kMaxDevices];
+    if (!smem_opted_in[d.index].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return LCE_ERR_CUDA;
-        smem_opted_in[d.index] = true;
+        smem_opted_in[d.index].store(true, std::memory_order_release);
     }
     const long long slots = d.sm_count / CG;  // one CTA per SM; a pair occupies the two SMs of a TPC
     const long long work = units * k_splits;
@@ -179,15 +213,24 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
 
 // CTA pairs cover two 128-row tiles at a time; with an odd, small number of row tiles the second
 // half of the last pair would idle, so such problems run on single CTAs.
-bool use_pair(long long M) {
+bool use_pair(long long M, int cg) {
     const long long m_tiles = cdiv(M, kBM);
-    return t_cta_group == 2 && (m_tiles % 2 == 0 || m_tiles >= 16);
+    return cg == 2 && (m_tiles % 2 == 0 || m_tiles >= 16);
 }
 
+// Which tcgen05 variant a call asks for: CTA pairs (cta_group::2) unless LCE_FLAG_ONE_CTA is set.
+inline int cta_group_of(unsigned flags) { return (flags & LCE_FLAG_ONE_CTA) ? 1 : 2; }
+
+// Kernel family of one call, decided once from the arguments and passed down (no per-thread state).
+struct Path {
+    bool use_tc;  // tcgen05 GEMM core (else the CUDA-core one)
+    int cg;       // cta group asked for: 2 = CTA pairs, 1 = single CTAs
+};
+
 template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
-int launch_tc(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
+int launch_tc(const DeviceInfo& d, int cg, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
               int m_fastest, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1) {
-    if (use_pair(M))
+    if (use_pair(M, cg))
         return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
     return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
 }
@@ -205,9 +248,9 @@ int choose_k_splits_simt(long long M, long long Nn, long long K) {
 // How many slices to cut the contraction of an M x Nn x K GEMM into so that a problem with few output
 // tiles still fills the GPU (the deterministic split-K: slices are added in slice order afterwards).
 // Uses a fixed SM count so that workspace sizes do not depend on the device.
-int choose_k_splits(long long M, long long Nn, long long K) {
-    const long long slots = use_pair(M) ? 74 : 148;
-    const long long units = cdiv(cdiv(M, kBM), use_pair(M) ? 2 : 1) * cdiv(Nn, kBN);
+int choose_k_splits(long long M, long long Nn, long long K, int cg) {
+    const long long slots = use_pair(M, cg) ? 74 : 148;
+    const long long units = cdiv(cdiv(M, kBM), use_pair(M, cg) ? 2 : 1) * cdiv(Nn, kBN);
     const long long k_blocks = cdiv(K, kBK);
     if (units == 0 || units * 2 > slots) return 1;
     long long s = slots / units;
@@ -263,7 +306,6 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // The tcgen05 path needs 16-bit inputs, 16-byte aligned bases and row pitches (H % 8 == 0).
 int choose_path(int dtype, long long H, const void* x, const void* w, unsigned flags, bool* use_tc) {
     const bool can_tc = dtype != LCE_DTYPE_F32 && (H % 8) == 0 && aligned16(x) && aligned16(w);
-    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
     if (flags & LCE_FLAG_FORCE_TC) {
         if (flags & LCE_FLAG_FORCE_SIMT) return LCE_ERR_ARG;
         if (dtype == LCE_DTYPE_F32) return LCE_ERR_ARG;
@@ -307,9 +349,11 @@ struct FwdOutputs {
 };
 
 template <class T>
-int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const void* w, const void* tgt,
+int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, const void* w, const void* tgt,
                        int tgt_i64, long long N, long long H, long long V, long long vocab_start,
                        const FwdOutputs& out, void* ws, cudaStream_t stream) {
+    const bool use_tc = path.use_tc;
+    const int cg = path.cg;
     const FwdLayout l = fwd_layout(N, V, use_tc);
     EpiStats::Params ep;
     ep.tgt = tgt;
@@ -324,7 +368,7 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiStats>(d, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream);
+            rc = launch_tc<false, false, kBf16, EpiStats>(d, cg, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream);
         } else {
             rc = LCE_ERR_ARG;
         }
@@ -347,9 +391,11 @@ int forward_stats_impl(const DeviceInfo& d, bool use_tc, const void* x, const vo
 
 // Greedy head: the forward GEMM with the argmax epilogue, then the per-row merge.
 template <class T>
-int greedy_head_impl(const DeviceInfo& d, bool use_tc, const void* x, const void* w, long long N, long long H,
+int greedy_head_impl(const DeviceInfo& d, const Path& path, const void* x, const void* w, long long N, long long H,
                      long long V, long long vocab_start, long long* token, float* logprob, float* lse, void* ws,
                      cudaStream_t stream) {
+    const bool use_tc = path.use_tc;
+    const int cg = path.cg;
     const FwdLayout l = fwd_layout(N, V, use_tc);
     EpiTop1::Params ep;
     ep.rows = static_cast<int>(N);
@@ -361,7 +407,7 @@ int greedy_head_impl(const DeviceInfo& d, bool use_tc, const void* x, const void
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiTop1>(d, a, b, N, V, H, 1, ep, stream);
+            rc = launch_tc<false, false, kBf16, EpiTop1>(d, cg, a, b, N, V, H, 1, ep, stream);
         } else {
             rc = LCE_ERR_ARG;
         }
@@ -444,8 +490,8 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     off += align_up(static_cast<size_t>(p.nr) * p.ldg * e, 256);
     p.off_dx_scratch = off;
     p.dx_slab_floats = cdiv(p.nr, 2 * kBM) * 2 * cdiv(H, p.bn) * kBM * p.bn;  // even tile count: CTA pairs
-    p.dx_splits = (need_dx && p.n_cblk == 1) ? (use_tc ? choose_k_splits(p.nr, H, p.nc) : choose_k_splits_simt(p.nr, H, p.nc)) : 1;
-    p.dw_splits = (need_dw && p.n_rblk == 1) ? (use_tc ? choose_k_splits(p.nc, H, p.nr) : choose_k_splits_simt(p.nc, H, p.nr)) : 1;
+    p.dx_splits = (need_dx && p.n_cblk == 1) ? (use_tc ? choose_k_splits(p.nr, H, p.nc, cta_group_of(flags)) : choose_k_splits_simt(p.nr, H, p.nc)) : 1;
+    p.dw_splits = (need_dw && p.n_rblk == 1) ? (use_tc ? choose_k_splits(p.nc, H, p.nr, cta_group_of(flags)) : choose_k_splits_simt(p.nc, H, p.nr)) : 1;
     if (need_dx && (p.n_cblk > 1 || p.dx_splits > 1))
         off += align_up(static_cast<size_t>(p.dx_splits) * p.dx_slab_floats * sizeof(float), 256);
     p.off_dw_scratch = off;
@@ -465,11 +511,13 @@ int store_mode(long long idx, long long count) {
 }
 
 template <class T, class TDx>
-int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void* x, const void* w,
+int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const void* x, const void* w,
                   const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
                   long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, void* const* dx_events,
                   const lce_peer_scatter* scatter, cudaStream_t stream) {
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
+    const bool use_tc = path.use_tc;
+    const int cg = path.cg;
     const T* xp = static_cast<const T*>(x);
     const T* wp = static_cast<const T*>(w);
     T* g = reinterpret_cast<T*>(ws + p.off_g);
@@ -499,7 +547,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 const Mat a{xp + r0 * H, nr, H, H}, b{wp + c0 * H, nc, H, H};
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<false, false, kBf16, EpiGrad<T>>(d, a, b, nr, nc, H, 1, ep, stream);
+                        rc = launch_tc<false, false, kBf16, EpiGrad<T>>(d, cg, a, b, nr, nc, H, 1, ep, stream);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiGrad<T>>(d, a, false, b, false, nr, nc, H, ep, stream);
@@ -534,7 +582,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 if (splits > 1) ep.mode = kStoreSlice;
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, gm, b, nr, H, nc, 0, ep, stream, splits);
+                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, cg, gm, b, nr, H, nc, 0, ep, stream, splits);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream, splits);
@@ -577,7 +625,7 @@ int backward_impl(const DeviceInfo& d, bool use_tc, const BwdPlan& p, const void
                 }
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, gm, b, nc, H, nr, 0, ep, stream, wsplits);
+                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, cg, gm, b, nc, H, nr, 0, ep, stream, wsplits);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream, wsplits);
@@ -665,11 +713,11 @@ int lce_forward_stats(const void* x, const void* w, const void* target, int targ
     fo.stats = stats;
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         case LCE_DTYPE_F16:
-            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         default:
-            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
     }
 }
 
@@ -689,11 +737,11 @@ int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t 
     long long* tok = reinterpret_cast<long long*>(token);
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return greedy_head_impl<__nv_bfloat16>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
         case LCE_DTYPE_F16:
-            return greedy_head_impl<__half>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
         default:
-            return greedy_head_impl<float>(*d, use_tc, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
     }
 }
 
@@ -760,13 +808,13 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
     fo.ignore_index = ignore_index;
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            rc = forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
             break;
         case LCE_DTYPE_F16:
-            rc = forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
             break;
         default:
-            rc = forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
     }
     if (rc) return rc;
     if (reduction != LCE_REDUCTION_NONE || valid_count) {
@@ -782,7 +830,6 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
 size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags,
                                     size_t block_bytes) {
     if (check_dims(N, H, V, dtype)) return 0;
-    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
     // the SIMT and tcgen05 plans differ only in scratch tiling; report the larger of the two
     const size_t a = plan_backward(N, H, V, dtype, true, flags, block_bytes).total;
     const size_t b = plan_backward(N, H, V, dtype, false, flags, block_bytes).total;
@@ -855,9 +902,9 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
 #define LCE_BWD(T)                                                                                          \
-    (dx32 ? backward_impl<T, float>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
+    (dx32 ? backward_impl<T, float>(*d, Path{use_tc, cta_group_of(flags)}, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
                                     dx, dw, wsc, flags, dx_events, scatter, s)                              \
-          : backward_impl<T, T>(*d, use_tc, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
+          : backward_impl<T, T>(*d, Path{use_tc, cta_group_of(flags)}, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
                                 dw, wsc, flags, dx_events, nullptr, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
@@ -875,7 +922,7 @@ int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t 
     int rc = device_info(&d);
     if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
+    const int cg = cta_group_of(flags);
     EpiStore<float>::Params ep;
     ep.out = out;
     ep.ldo = N;
@@ -888,8 +935,8 @@ int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t 
     const Mat am = a_mn ? Mat{a, K, M, M} : Mat{a, M, K, K};
     const Mat bm = b_mn ? Mat{b, K, N, N} : Mat{b, N, K, K};
 #define LCE_DBG(AMN, BMN)                                                                               \
-    (dtype == LCE_DTYPE_BF16 ? launch_tc<AMN, BMN, true, EpiStore<float>>(*d, am, bm, M, N, K, 1, ep, s) \
-                             : launch_tc<AMN, BMN, false, EpiStore<float>>(*d, am, bm, M, N, K, 1, ep, s))
+    (dtype == LCE_DTYPE_BF16 ? launch_tc<AMN, BMN, true, EpiStore<float>>(*d, cg, am, bm, M, N, K, 1, ep, s) \
+                             : launch_tc<AMN, BMN, false, EpiStore<float>>(*d, cg, am, bm, M, N, K, 1, ep, s))
     if (!a_mn && !b_mn) return LCE_DBG(false, false);
     if (!a_mn && b_mn) return LCE_DBG(false, true);
     if (a_mn && !b_mn) return LCE_DBG(true, false);
@@ -956,11 +1003,11 @@ int lce_forward_stats_static(const void* x, const void* w, const void* target, i
     // the merge kernel reads, earlier in this same call and on the same stream.
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return forward_stats_impl<__nv_bfloat16>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
+            return forward_stats_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
         case LCE_DTYPE_F16:
-            return forward_stats_impl<__half>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
+            return forward_stats_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
         default:
-            return forward_stats_impl<float>(*d, use_tc, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
+            return forward_stats_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, scratch, s);
     }
 }
 
@@ -991,6 +1038,32 @@ extern "C" int lce_dx_reduce_gather(const void* staging, int world, int rank, in
         case LCE_DTYPE_BF16: dx_reduce_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
         case LCE_DTYPE_F16: dx_reduce_gather_kernel<__half><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
         case LCE_DTYPE_F32: dx_reduce_gather_kernel<float><<<blocks, 256, 0, s>>>(st, world, rpr, H, row0, n_rows, outs); break;
+        default: return LCE_ERR_ARG;
+    }
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+extern "C" int lce_dx_reduce_slice(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
+                                   void* out, void* stream) {
+    if (!staging || !out || world < 1 || world > kMaxPeers || rank < 0 || rank >= world || N <= 0 || H <= 0 ||
+        (H % 4) != 0 || !aligned16(staging) || !aligned16(out))
+        return LCE_ERR_ARG;
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const long long rpr = cdiv(N, world);
+    const long long row0 = rpr * rank;
+    const long long n_rows = row0 >= N ? 0 : (N - row0 < rpr ? N - row0 : rpr);
+    if (n_rows == 0) return LCE_OK;
+    const long long quads = n_rows * (H / 4);
+    const int blocks = static_cast<int>(cdiv(quads, 256) < 148 * 16 ? cdiv(quads, 256) : 148 * 16);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float* st = static_cast<const float*>(staging);
+    switch (dtype) {
+        case LCE_DTYPE_BF16: dx_reduce_slice_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(st, world, rpr, H, n_rows, static_cast<__nv_bfloat16*>(out)); break;
+        case LCE_DTYPE_F16: dx_reduce_slice_kernel<__half><<<blocks, 256, 0, s>>>(st, world, rpr, H, n_rows, static_cast<__half*>(out)); break;
+        case LCE_DTYPE_F32: dx_reduce_slice_kernel<float><<<blocks, 256, 0, s>>>(st, world, rpr, H, n_rows, static_cast<float*>(out)); break;
         default: return LCE_ERR_ARG;
     }
     LCE_COUNT_LAUNCH();
@@ -1156,6 +1229,7 @@ namespace {
 
 struct MatmulPlan {
     bool use_tc;
+    int cg;
     int splits;
     long long slab_floats;
     size_t ws_bytes;
@@ -1163,9 +1237,9 @@ struct MatmulPlan {
 
 MatmulPlan plan_matmul(long long M, long long N, long long K, int dtype, bool aligned, unsigned flags) {
     MatmulPlan p;
-    t_cta_group = (flags & LCE_FLAG_ONE_CTA) ? 1 : 2;
+    p.cg = cta_group_of(flags);
     p.use_tc = dtype != LCE_DTYPE_F32 && aligned && !(flags & LCE_FLAG_FORCE_SIMT);
-    p.splits = p.use_tc ? choose_k_splits(M, N, K) : 1;
+    p.splits = p.use_tc ? choose_k_splits(M, N, K, p.cg) : 1;
     p.slab_floats = cdiv(M, 2 * kBM) * 2 * cdiv(N, kBN) * kBM * kBN;
     p.ws_bytes = p.splits > 1 ? static_cast<size_t>(p.splits) * p.slab_floats * sizeof(float) : 0;
     return p;
@@ -1189,10 +1263,10 @@ int matmul_impl(const DeviceInfo& d, const MatmulPlan& p, const Mat& a, bool a_m
         constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
         // tiles that run together share a B panel when there are many row tiles, an A panel otherwise
         const int m_fastest = cdiv(M, kBM) >= cdiv(N, kBN) ? 1 : 0;
-        if (!a_mn && !b_mn) rc = launch_tc<false, false, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
-        else if (!a_mn && b_mn) rc = launch_tc<false, true, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
-        else if (a_mn && !b_mn) rc = launch_tc<true, false, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
-        else rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        if (!a_mn && !b_mn) rc = launch_tc<false, false, kBf16, EpiStore<T>>(d, p.cg, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else if (!a_mn && b_mn) rc = launch_tc<false, true, kBf16, EpiStore<T>>(d, p.cg, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else if (a_mn && !b_mn) rc = launch_tc<true, false, kBf16, EpiStore<T>>(d, p.cg, a, b, M, N, K, m_fastest, ep, s, p.splits);
+        else rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, p.cg, a, b, M, N, K, m_fastest, ep, s, p.splits);
         if (rc == LCE_OK && p.splits > 1) {
             const int m_tiles = static_cast<int>(cdiv(M, kBM)), n_tiles = static_cast<int>(cdiv(N, kBN));
             const long long quads = static_cast<long long>(m_tiles) * n_tiles * (kBN / 4) * kBM;

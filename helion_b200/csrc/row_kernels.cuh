@@ -275,4 +275,34 @@ __global__ void dx_reduce_gather_kernel(const float* __restrict__ staging, int w
     }
 }
 
+// The reduce half alone: sums the `world` staging slots of this rank's row slice in rank order, rounds once
+// and writes the slice to LOCAL memory (out is [rows_per_rank, H]); an all-gather by the caller follows.
+template <class T>
+__global__ void dx_reduce_slice_kernel(const float* __restrict__ staging, int world, long long rows_per_rank,
+                                       long long H, long long n_rows, T* __restrict__ out) {
+    const long long quads_per_row = H / 4;
+    const long long total = n_rows * quads_per_row;
+    const long long slot_floats = rows_per_rank * H;
+    for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < total;
+         q += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float* src = staging + q * 4;
+        float4 acc = *reinterpret_cast<const float4*>(src);
+        for (int k = 1; k < world; ++k) {
+            const float4 v = *reinterpret_cast<const float4*>(src + k * slot_floats);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        T* dst = out + q * 4;
+        if constexpr (sizeof(T) == 2) {
+            alignas(8) T packed[4] = {Cvt<T>::from_f(acc.x), Cvt<T>::from_f(acc.y), Cvt<T>::from_f(acc.z),
+                                      Cvt<T>::from_f(acc.w)};
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(packed);
+        } else {
+            *reinterpret_cast<float4*>(dst) = acc;
+        }
+    }
+}
+
 }  // namespace lce

@@ -25,7 +25,7 @@ def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int 
                 return_logsumexp: bool = False, process_group=None):
     """``(token, logprob)`` - int64 index of the largest logit of every row (lowest index on ties, offset by
     ``vocab_start``) and float32 ``log_softmax`` at it; with ``return_logsumexp`` also the row's logsumexp.
-    ``vocab_start`` defaults to 0, or to ``rank * weight.shape[0]`` when a ``process_group`` is given."""
+    ``vocab_start`` defaults to 0, or with a ``process_group`` to the sum of the lower ranks' shard heights."""
     _need_cuda("hidden", hidden)
     _need_cuda("weight", weight)
     _need_dtype("hidden", hidden, FLOAT_DTYPES)
@@ -52,7 +52,7 @@ def greedy_head(hidden: torch.Tensor, weight: torch.Tensor, *, vocab_start: int 
     dev = hidden.device
     rank, world = parallel.group_rank_size(process_group)
     if vocab_start is None:
-        vocab_start = rank * vocab_size
+        vocab_start = parallel.shard_start(process_group, vocab_size, hidden.device)
     token = torch.empty(shape, dtype=torch.int64, device=dev)
     logprob = torch.empty(shape, dtype=torch.float32, device=dev)
     lse = torch.empty(shape, dtype=torch.float32, device=dev) if return_logsumexp or world > 1 else None

@@ -172,9 +172,12 @@ def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
-def _resolve_vocab_start(vocab_start: int | None, rank: int, v_local: int) -> int:
-    # contiguous equal shards unless the caller says where this shard begins
-    return rank * v_local if vocab_start is None else int(vocab_start)
+def _resolve_vocab_start(vocab_start: int | None, process_group: Any, v_local: int, device: torch.device) -> int:
+    """Where this rank's shard begins: what the caller says, else the sum of the lower ranks' shard heights
+    (``rank * v_local`` for equal shards; uneven shards, as ``parallel.shard_weight`` cuts them, differ)."""
+    if vocab_start is not None:
+        return int(vocab_start)
+    return parallel.shard_start(process_group, v_local, device)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -258,7 +261,7 @@ def _forward(hidden: torch.Tensor, weight: torch.Tensor, target: torch.Tensor, r
     target1d = target.view(n_rows)
     if world == 1 and vocab_start in (None, 0):
         return _forward_single(hidden2d, weight, target1d, target.shape, red, ignore_index)
-    stats = local_stats(hidden2d, weight, target1d, _resolve_vocab_start(vocab_start, rank, v_local),
+    stats = local_stats(hidden2d, weight, target1d, _resolve_vocab_start(vocab_start, process_group, v_local, dev),
                         _path_flags())
     loss, lse, _ = finalize(parallel.gather_stats(stats, process_group), target1d, reduction, ignore_index)
     if red == _lib.REDUCTION_NONE:
@@ -293,9 +296,6 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
         # reference: empty dX and an all-zero dW (tritium/ops/cross_entropy.py:911-913)
         return (torch.empty_like(hidden2d) if need_dx else None,
                 torch.zeros_like(weight) if need_dw else None)
-    dx = None
-    if need_dx:
-        dx = torch.empty((n_rows, hidden_size), dtype=torch.float32 if sharded else hidden2d.dtype, device=dev)
     dw = torch.empty_like(weight) if need_dw else None
 
     if grad_out.dtype != torch.float32:
@@ -303,7 +303,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     grad_out = grad_out.contiguous()
     dtype = _DTYPE_CODE[hidden2d.dtype]
     block = _block_bytes()
-    vstart = _resolve_vocab_start(vocab_start, rank, v_local)
+    vstart = _resolve_vocab_start(vocab_start, process_group, v_local, dev)
     ws = _workspace(L.lce_backward_workspace_bytes(n_rows, hidden_size, v_local, dtype, flags, block), dev)
 
     # Sharded: two ways to sum the partial dX over the group.
@@ -312,8 +312,8 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     #        Falls back to "nccl" for the whole group if peer-mapped memory cannot be set up.
     #  "nccl": fp32 partial dX per row chunk, all-reduced on a side stream as soon as the library signals
     #        the chunk final, while the remaining dW GEMMs run on the main stream.
-    events, event_array, chunk_rows, scatter, peers = None, None, n_rows, None, None
-    if sharded and dx is not None:
+    events, event_array, chunk_rows, scatter, peers, staging_index = None, None, n_rows, None, None, 0
+    if sharded and need_dx:
         plan = (ctypes.c_int64 * 4)()
         _lib.check(L.lce_backward_plan(n_rows, hidden_size, v_local, dtype, flags, block, hidden2d.data_ptr(),
                                        weight.data_ptr(), plan), "lce_backward_plan")
@@ -321,13 +321,21 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
         events = parallel.ready_events(dev, n_chunks)
         event_array = (ctypes.c_void_p * n_chunks)(*[e.cuda_event for e in events])
         if _dx_reduce_mode() == "p2p" and hidden_size % 4 == 0 and world <= 8:
-            peers = parallel.peer_buffers(process_group, n_rows, hidden_size, hidden2d.dtype, dev)
+            peers = parallel.peer_buffers(process_group, n_rows, hidden_size, dev)
         if peers is not None:
+            staging_index = peers.next_buffer()
             scatter = _lib.PeerScatter()
-            for k, ptr in enumerate(peers.staging_ptrs):
+            for k, ptr in enumerate(peers.staging_ptrs[staging_index]):
                 scatter.staging[k] = ptr
             scatter.rank, scatter.world = rank, world
-            dx = None  # nothing is written locally: rows leave through the epilogue
+        elif not parallel.ranks_agree(process_group, ("dx-chunks", n_rows, hidden_size, dtype, flags, block),
+                                      (chunk_rows, n_chunks), dev):
+            # each rank plans its row chunks from its own shard height; if the plans differ (uneven shards
+            # at a plan boundary) chunk-wise collectives would not match up: reduce dX in one piece instead
+            events, chunk_rows = events[-1:], n_rows
+    dx = None
+    if need_dx and peers is None:  # with peer buffers nothing is written locally: rows leave through the epilogue
+        dx = torch.empty((n_rows, hidden_size), dtype=torch.float32 if sharded else hidden2d.dtype, device=dev)
 
     with _on_device(dev):
         _lib.check(
@@ -339,7 +347,7 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
             "lce_backward",
         )
     if peers is not None:
-        dx = _finish_peer_reduce(peers, events, n_rows, hidden_size, dtype, dev)
+        dx = _finish_peer_reduce(peers, staging_index, events, n_rows, hidden_size, hidden2d.dtype, dev)
     elif sharded and dx is not None:
         dx = parallel.reduce_dx_chunks(dx, chunk_rows, events, hidden2d.dtype, process_group)
     return dx, dw
@@ -349,23 +357,31 @@ def _dx_reduce_mode() -> str:
     return os.environ.get("HELION_B200_DX_REDUCE", "p2p")
 
 
-def _finish_peer_reduce(peers, events, n_rows: int, hidden_size: int, dtype: int, dev: torch.device) -> torch.Tensor:
+def _finish_peer_reduce(peers, staging_index: int, events, n_rows: int, hidden_size: int, dtype: torch.dtype,
+                        dev: torch.device) -> torch.Tensor:
     """Second half of the fused dX reduction, on the side stream so that it overlaps the remaining dW GEMMs:
-    once this rank's last dX rows have left (event), order the ranks, sum + all-gather, order again."""
+    once this rank's last dX rows have left (event), one 4-byte all-reduce orders the ranks (every rank's
+    partial rows have landed in their owners' staging buffers), this rank sums the slots of its own row
+    slice, and an all-gather of the rounded slices gives every rank the whole dX."""
+    import torch.distributed as dist
+
     L = _lib.lib()
     main = torch.cuda.current_stream(dev)
     side = parallel.comm_stream(dev)
     side.wait_event(events[-1])
+    rpr = -(-n_rows // peers.world)
     with torch.cuda.stream(side):
-        peers.order_ranks()  # every rank's partial rows have landed in their owners' staging buffers
-        out_ptrs = (ctypes.c_void_p * peers.world)(*peers.final_ptrs)
-        _lib.check(L.lce_dx_reduce_gather(peers.staging.data_ptr(), peers.world, peers.rank, n_rows, hidden_size, dtype,
-                                          out_ptrs, side.cuda_stream), "lce_dx_reduce_gather")
-        peers.order_ranks()  # every rank's slice has been stored everywhere; staging may be reused
-        dx = peers.final.clone()
+        peers.order_ranks()
+        piece = torch.empty((rpr, hidden_size), dtype=dtype, device=dev)
+        gathered = torch.empty((peers.world * rpr, hidden_size), dtype=dtype, device=dev)
+        _lib.check(L.lce_dx_reduce_slice(peers.staging[staging_index].data_ptr(), peers.world, peers.rank, n_rows,
+                                         hidden_size, _DTYPE_CODE[dtype], piece.data_ptr(), side.cuda_stream),
+                   "lce_dx_reduce_slice")
+        dist.all_gather_into_tensor(gathered, piece, group=peers.group)
     main.wait_stream(side)
-    dx.record_stream(main)
-    return dx
+    piece.record_stream(main)
+    gathered.record_stream(main)
+    return gathered[:n_rows]
 
 
 def linear_cross_entropy_backward(

@@ -134,30 +134,52 @@ def reduce_dx_chunks(dx_partial: torch.Tensor, chunk_rows: int, events, out_dtyp
 
 # ---- dX reduce-scatter fused into the GEMM epilogue (peer stores over NVLink) ----------------------
 class PeerBuffers:
-    """Symmetric (peer-mapped) buffers of one (group, N, H, dtype) problem, allocated once and reused:
+    """Symmetric (peer-mapped) staging buffers of one (group, H, device), allocated once for a capacity
+    in rows and reused by every problem that fits:
 
-    * ``staging``  [world, rows_per_rank, H] fp32 on every rank: rank r's dX epilogue stores the partial
-      rows owned by rank o into slot r of rank o's staging buffer;
-    * ``final``    [N, H] in the op dtype on every rank: the owner of a row slice sums its ``world`` slots
-      and stores the rounded result into every rank's ``final``.
+    * two ``staging`` buffers ``[world, rows_per_rank, H]`` fp32 on every rank: rank r's dX epilogue stores
+      the partial rows owned by rank o into slot r of rank o's staging buffer. Calls alternate between
+      the two buffers.
 
-    Two tiny all-reduces order the ranks (everyone has scattered before anyone sums; everyone has
-    gathered before the buffers are reused). No kernel of this package waits on another GPU.
+    One 4-byte all-reduce per call orders the ranks (everyone has scattered before anyone sums). The
+    owner then sums the ``world`` slots of its row slice in rank order, rounds once, and an NCCL
+    all-gather hands every rank the whole dX. Why two buffers make a second barrier unnecessary: a rank
+    scatters into buffer b again two calls later, after it has passed the barrier of the call in
+    between, which every rank enters only after it has finished summing buffer b (same stream).
+    No kernel of this package waits on another GPU, and nothing here uses an NVLink multicast object:
+    the buffers are only ever written with plain peer stores, so multicast binding is switched off
+    for the allocation (a rank that exits while its memory is bound to a multicast object can raise
+    NVLink faults on its peers).
     """
 
-    def __init__(self, process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype, device: torch.device):
+    def __init__(self, process_group: Any, capacity_rows: int, hidden: int, device: torch.device):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self.rank, self.world = group_rank_size(process_group)
         self.group = process_group
-        self.rows_per_rank = -(-n_rows // self.world)
-        self.staging = symm_mem.empty((self.world, self.rows_per_rank, hidden), dtype=torch.float32, device=device)
-        self.final = symm_mem.empty((n_rows, hidden), dtype=dtype, device=device)
-        self._staging_handle = symm_mem.rendezvous(self.staging, process_group)
-        self._final_handle = symm_mem.rendezvous(self.final, process_group)
-        self.staging_ptrs = [int(p) for p in self._staging_handle.buffer_ptrs]
-        self.final_ptrs = [int(p) for p in self._final_handle.buffer_ptrs]
+        self.hidden = hidden
+        self.capacity_rows = capacity_rows
+        slot_rows = -(-capacity_rows // self.world)
+        self.staging, self.staging_ptrs = [], []
+        self._handles = []
+        for _ in range(2):
+            buf = symm_mem.empty((self.world * slot_rows * hidden,), dtype=torch.float32, device=device)
+            handle = symm_mem.rendezvous(buf, process_group)
+            self.staging.append(buf)
+            self._handles.append(handle)
+            self.staging_ptrs.append([int(p) for p in handle.buffer_ptrs])
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.calls = 0
+
+    def next_buffer(self) -> int:
+        """Index (0 / 1) of the staging buffer this call scatters into; alternates call by call, in the
+        same order on every rank because every rank makes the same sequence of calls."""
+        b = self.calls & 1
+        self.calls += 1
+        return b
 
     def order_ranks(self) -> None:
         """Stream-ordered barrier: a 4-byte all-reduce on the current stream."""
@@ -169,20 +191,83 @@ class PeerBuffers:
 _peer_buffers: dict[tuple, PeerBuffers | None] = {}
 
 
-def peer_buffers(process_group: Any, n_rows: int, hidden: int, dtype: torch.dtype,
-                 device: torch.device) -> PeerBuffers | None:
-    """The cached peer buffers of this problem, or None if peer-mapped memory cannot be set up on this
-    machine. The decision is collective (a MIN all-reduce over the group), so either every rank takes the
-    fused path or every rank takes the NCCL path."""
-    key = (id(process_group), n_rows, hidden, dtype, device.index)
-    if key not in _peer_buffers:
+def peer_buffers(process_group: Any, n_rows: int, hidden: int, device: torch.device) -> PeerBuffers | None:
+    """The cached peer buffers that hold ``n_rows`` rows of ``hidden`` floats, or None if peer-mapped
+    memory cannot be set up on this machine. One pair of buffers per (group, hidden, device): a batch of
+    fewer rows reuses it, a larger one replaces it (collectively - every rank sees the same ``n_rows``),
+    so variable-length batches neither leak symmetric memory nor rendezvous again. The decision to use the
+    fused path is collective too (a MIN all-reduce over the group), so either every rank takes it or
+    every rank takes the NCCL path."""
+    key = (id(process_group), hidden, device.index)
+    have = _peer_buffers.get(key, False)
+    if have is None:
+        return None
+    if have is False or have.capacity_rows < n_rows:
         import torch.distributed as dist
 
+        _peer_buffers.pop(key, None)  # drop the smaller pair before its replacement is allocated
+        del have
         try:
-            bufs = PeerBuffers(process_group, n_rows, hidden, dtype, device)
+            bufs = PeerBuffers(process_group, n_rows, hidden, device)
         except Exception:  # noqa: BLE001 - e.g. no peer access between these GPUs
             bufs = None
         agreed = torch.tensor([1.0 if bufs is not None else 0.0], device=device)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=process_group)
         _peer_buffers[key] = bufs if float(agreed.item()) == 1.0 else None
     return _peer_buffers[key]
+
+
+# ---- where a shard begins, and whether the ranks agree on a plan ---------------------------------------
+_shard_starts: dict[tuple, int] = {}
+_agreements: dict[tuple, bool] = {}
+
+
+def shard_start(process_group: Any, v_local: int, device: torch.device) -> int:
+    """First global vocabulary row of this rank's shard when the caller did not say: the sum of the shard
+    heights of the lower ranks (one small all-gather the first time a (group, height) pair is seen).
+    With equal shards this is ``rank * v_local``; with the uneven shards of ``shard_weight`` it is not."""
+    rank, world = group_rank_size(process_group)
+    if world == 1:
+        return 0
+    key = (id(process_group), v_local)
+    if key not in _shard_starts:
+        import torch.distributed as dist
+
+        mine = torch.tensor([v_local], dtype=torch.int64, device=device)
+        heights = torch.empty((world,), dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(heights, mine, group=process_group)
+        _shard_starts[key] = int(heights[:rank].sum().item())
+    return _shard_starts[key]
+
+
+def ranks_agree(process_group: Any, key: tuple, values: tuple[int, ...], device: torch.device) -> bool:
+    """True if every rank of the group passes the same ``values`` (checked once per ``key`` with one small
+    all-gather). Used before a sequence of collectives whose count and sizes each rank derives locally."""
+    rank, world = group_rank_size(process_group)
+    if world == 1:
+        return True
+    full_key = (id(process_group),) + key
+    if full_key not in _agreements:
+        import torch.distributed as dist
+
+        mine = torch.tensor(values, dtype=torch.int64, device=device)
+        everyone = torch.empty((world * len(values),), dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(everyone, mine, group=process_group)
+        _agreements[full_key] = bool((everyone.view(world, len(values)) == mine).all().item())
+    return _agreements[full_key]
+
+
+def gather_rows(local_rows: torch.Tensor, n_rows: int, process_group: Any) -> torch.Tensor:
+    """All-gather of row slices: rank r holds rows ``[r * rpr, (r+1) * rpr)`` of an ``[n_rows, ...]`` tensor
+    (rpr = ceil(n_rows / world); the last ranks' slices may be short or empty but arrive padded to rpr rows).
+    Returns the full tensor on every rank. Used to rebuild activations that were copied to the GPUs one
+    slice per rank, so that a batch crosses the host link once instead of once per GPU."""
+    rank, world = group_rank_size(process_group)
+    if world == 1:
+        return local_rows[:n_rows]
+    import torch.distributed as dist
+
+    rpr = local_rows.shape[0]
+    out = torch.empty((world * rpr,) + tuple(local_rows.shape[1:]), dtype=local_rows.dtype, device=local_rows.device)
+    dist.all_gather_into_tensor(out, local_rows.contiguous(), group=process_group)
+    return out[:n_rows]

@@ -9,7 +9,9 @@
  *
  * Conventions
  *   - every pointer is a device pointer owned by the caller unless stated otherwise; the library
- *     allocates nothing and keeps no reference after the call returns;
+ *     allocates nothing at call time and keeps no reference after the call returns. The one piece of
+ *     device memory it owns is compiled into its image: the 16 MiB scratch array of
+ *     lce_forward_stats_static (plus a 4-byte status word), held by every GPU that loads the library;
  *   - a call only enqueues work on `stream` (a cudaStream_t passed as void*) of the current
  *     device and returns; it never synchronises;
  *   - return value 0 = enqueued; anything else is a synchronous argument / launch error, see
@@ -95,7 +97,7 @@ int lce_forward_stats(const void* x, const void* w, const void* target, int targ
  * the device or through any library.
  *
  *   - Limit: ceil(V_local / T) * 3 * roundup(N, 64) * 4 bytes must fit in the 16 MiB, with T = 256 on
- *     the tcgen05 path and 32 on the CUDA-core path (e.g. N = 4096 with V_local = 50304 in bf16).
+ *     the tcgen05 path and T = 128 on the CUDA-core path (e.g. N = 4096 with V_local = 50304 in bf16).
  *     Larger problems return LCE_ERR_STATIC_SCRATCH and launch nothing.
  *   - The first call on each device looks up the array's device address (with that device current);
  *     make that first call outside any stream capture. Later calls reuse the cached address.
@@ -165,6 +167,16 @@ typedef struct {
 int lce_dx_reduce_gather(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
                          void* const* out_ptrs, void* stream);
 
+/* The reduce half alone: sums the world slots of this rank's row slice (rows rank * rows_per_rank ..) of
+ * ITS OWN staging buffer in rank order, rounds once and writes the slice to local memory, out =
+ * [rows_per_rank, H] in `dtype`, 16-byte aligned. The caller then all-gathers the slices (any collective
+ * library), which also tells every rank that all slices are final. New; the reference is single-GPU. */
+int lce_dx_reduce_slice(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
+                        void* out, void* stream);
+
+/* Workspace sizes and the split of a short contraction over CTAs are computed for a GPU of 148 SMs
+ * (74 CTA pairs), B200's count, whatever device is current: the plan, and with it the summation order
+ * and the result bits, are then the same on every device the library accepts. */
 size_t lce_backward_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags,
                                     size_t block_bytes);
 int lce_backward(const void* x, const void* w, const void* target, int target_is_i64,
@@ -260,7 +272,9 @@ int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, cons
                          const void* dresidual, void* dx, void* dweight, int64_t n_rows, int64_t hidden, float eps,
                          int dtype, void* ws, size_t ws_bytes, void* stream);
 
-/* ---- test hook -------------------------------------------------------------------------------
+/* ---- test hook (not part of the product interface) -------------------------------------------
+ * Test infrastructure only: nothing above depends on it, a binding for the reference needs no stub
+ * for it, and it may change without notice.
  * out[M, N] (float32, row-major) = A * B^T on the tcgen05 GEMM core used by every kernel above,
  * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b
  * with N. No counterpart in the reference; exists so the operand-layout handling can be tested

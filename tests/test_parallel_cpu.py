@@ -49,6 +49,21 @@ def _worker(rank: int, world: int, port: int, scenario: str, results) -> None:
             return  # leaves between steps, with nothing in flight
         w_loc, start = parallel.shard_weight(w, dist.group.WORLD)
         assert (start, start + w_loc.shape[0]) == parallel.shard_bounds(w.shape[0], world, rank)
+        # 1003 rows over two ranks are 502 + 501: the default start of rank 1 is 502, not rank * 501
+        cpu = torch.device("cpu")
+        assert parallel.shard_start(dist.group.WORLD, w_loc.shape[0], cpu) == start
+        assert parallel.shard_start(dist.group.WORLD, w_loc.shape[0], cpu) == start  # cached: no second collective
+        # plans derived from the local shard height: equal values agree, rank-dependent ones do not
+        assert parallel.ranks_agree(dist.group.WORLD, ("same",), (96, 3), cpu)
+        assert not parallel.ranks_agree(dist.group.WORLD, ("differ",), (96, 3 + rank), cpu)
+        # a batch copied to the ranks one row slice each is rebuilt by one all-gather (96 rows -> 48 + 48;
+        # 95 rows -> 48 + 47 padded to 48)
+        for n in (96, 95):
+            rpr = -(-n // world)
+            piece = torch.zeros(rpr, 40, dtype=x.dtype)
+            mine = x[:n][rank * rpr:(rank + 1) * rpr]
+            piece[:mine.shape[0]] = mine
+            assert torch.equal(parallel.gather_rows(piece, n, dist.group.WORLD), x[:n])
         stats = parallel.gather_stats(oracle.shard_stats(x, w_loc, t, start), dist.group.WORLD)
         assert stats.shape == (world, 3, 96)
         merged = oracle.merge_stats(stats, t)
