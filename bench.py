@@ -148,10 +148,28 @@ def build_workload(name: str):
     return inputs.CONFIGS[name]
 
 
+def workload_config(cfg, world: int, reduction: str) -> dict:
+    """The `config` object of the JSON line; both arms (ours and --impl reference) print the same keys."""
+    v_loc = cfg.vocab // world
+    return {"workload": cfg.name, "tokens": cfg.rows, "hidden": cfg.hidden, "vocab": cfg.vocab,
+            "vocab_per_gpu": v_loc, "reduction": reduction, "parallelism": f"vocab-parallel x{world}",
+            "l2": "weight shard (%.0f MB) exceeds L2, no explicit flush" % (v_loc * cfg.hidden * 2 / 1e6)}
+
+
+def host_threads() -> int:
+    """Host cores this process may use (its CPU affinity), whatever OMP_NUM_THREADS a launcher exported."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(data: dict, sample_rows: int, repeats: int, warmup: int) -> dict:
     """fp32 ground-truth expression on the host cores over the first `sample_rows` rows x full vocab."""
     from oracle import oracle
 
+    # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm uses every core it may at every GPU count
+    torch.set_num_threads(host_threads())
     h = data["hidden"].reshape(-1, data["hidden"].shape[-1])[:sample_rows]
     t = data["target"].reshape(-1)[:sample_rows]
     red = data["reduction"]
@@ -195,8 +213,7 @@ def run_reference(args) -> None:
         "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens": cfg.rows, "hidden": cfg.hidden, "vocab": cfg.vocab,
-                   "reduction": cfg.reduction, "sample_rows": sample_rows},
+        "config": workload_config(cfg, max(1, args.gpus), cfg.reduction),
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "host_cpus", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -205,7 +222,7 @@ def run_reference(args) -> None:
 
 
 def run_ours(args) -> None:
-    from helion_b200 import _lib, inputs, ops
+    from helion_b200 import _lib, inputs, ops, parallel
 
     rank, world, local, dist = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
@@ -253,12 +270,27 @@ def run_ours(args) -> None:
         return float(tt.item())
 
     # ---- device-resident timing ------------------------------------------------------------
+    # Warm-up by step count, then by time: a GPU that has idled starts at its boost clock and settles to the
+    # clock its power cap sustains only after a second or two of load. Short timed regions (8 GPUs: tens of
+    # milliseconds) would otherwise be measured at a clock a training run never sees.
     for _ in range(max(args.warmup, 3)):
         loss = step(x, t)
     barrier()
+    preheat_steps = 0
+    t_heat = time.perf_counter()
+    while args.preheat_s > 0:
+        for _ in range(5):
+            loss = step(x, t)
+        preheat_steps += 5
+        torch.cuda.synchronize()
+        go_on = torch.tensor([1.0 if time.perf_counter() - t_heat < args.preheat_s else 0.0], device=dev)
+        if world > 1:  # every rank leaves the loop after the same number of steps
+            dist.all_reduce(go_on, op=dist.ReduceOp.MIN)
+        if float(go_on.item()) == 0.0:
+            break
+    preheat_s = time.perf_counter() - t_heat
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()  # every rank samples its own GPU
     launches0 = L.lce_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -268,28 +300,56 @@ def run_ours(args) -> None:
     e1.record()
     barrier()
     launches = L.lce_launch_count() - launches0
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop() if rank == 0 else None
+    ms_local = e0.elapsed_time(e1)
+    ms_total = max_over_ranks(ms_local)
+    clocks = sampler.stop()
     ms_step = ms_total / args.steps
     loss_value = float(loss.float().mean().item())
+    # time x clock per rank: what the step costs in SM cycles, comparable across runs at different clocks
+    my_mhz = float(clocks["sm_mhz"] or 0.0)
+    per_rank = [(ms_local / args.steps, my_mhz)]
+    if world > 1:
+        mine = torch.tensor([ms_local / args.steps, my_mhz], dtype=torch.float64, device=dev)
+        everyone = torch.empty((world, 2), dtype=torch.float64, device=dev)
+        dist.all_gather_into_tensor(everyone.view(-1), mine)
+        per_rank = [(float(a), float(b)) for a, b in everyone.tolist()]
+    reasons = clocks["reasons"]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, reasons)
+        reasons = sorted({r for rr in gathered for r in rr})
 
     # ---- end to end: every step's activations and labels come from pinned host memory and its loss goes
     # back to the host, all inside the timed region. As in a training loop with a prefetching loader, the
-    # copy of step i+1 runs on a copy stream while step i computes (two device buffers).
+    # copy of step i+1 runs on a copy stream while step i computes (two device buffers). With several GPUs
+    # the batch crosses the host link ONCE: rank r copies rows [r * N/R, (r+1) * N/R) and one all-gather over
+    # NVLink rebuilds the batch on every rank (replicating it by R host copies made the copy the bottleneck).
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
+    rpr = -(-n // world)
+    r0, r1 = min(n, rank * rpr), min(n, (rank + 1) * rpr)
+    x2d_host, t1d_host = x_host.view(n, h), t_host.view(n)
     xb = [torch.empty_like(x).requires_grad_(True) for _ in range(2)]
     tb = [torch.empty_like(t) for _ in range(2)]
+    x_piece = torch.zeros((rpr, h), dtype=x.dtype, device=dev)
+    t_piece = torch.zeros((rpr,), dtype=t.dtype, device=dev)
     ready = [torch.cuda.Event() for _ in range(2)]     # copy into buffer b has landed
     consumed = [torch.cuda.Event() for _ in range(2)]  # step using buffer b has finished
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    h2d_bytes = (r1 - r0) * (h * x.element_size() + t.element_size())
 
     def prefetch(b):
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[b])
             with torch.no_grad():
-                xb[b].copy_(x_host, non_blocking=True)
-                tb[b].copy_(t_host, non_blocking=True)
+                if world == 1:
+                    xb[b].copy_(x_host, non_blocking=True)
+                    tb[b].copy_(t_host, non_blocking=True)
+                else:
+                    x_piece[:r1 - r0].copy_(x2d_host[r0:r1], non_blocking=True)
+                    t_piece[:r1 - r0].copy_(t1d_host[r0:r1], non_blocking=True)
+                    xb[b].view(n, h).copy_(parallel.gather_rows(x_piece, n, group))
+                    tb[b].view(n).copy_(parallel.gather_rows(t_piece, n, group))
             ready[b].record(copy_stream)
 
     def run_e2e(steps):
@@ -307,6 +367,8 @@ def run_ours(args) -> None:
 
     run_e2e(3)
     barrier()
+    # the batch every rank computed on is the batch the host holds
+    assert torch.equal(xb[0].detach(), x.detach()) and torch.equal(tb[0], t), "gathered batch differs from the host batch"
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     run_e2e(args.steps)
@@ -357,9 +419,8 @@ def run_ours(args) -> None:
         "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens": n, "hidden": h, "vocab": v, "vocab_per_gpu": v_loc,
-                   "reduction": red, "parallelism": f"vocab-parallel x{world}",
-                   "l2": "weight shard (%.0f MB) exceeds L2, no explicit flush" % (v_loc * h * 2 / 1e6)},
+        "config": workload_config(cfg, world, red),
+        "preheat_s": round(preheat_s, 3), "preheat_steps": preheat_steps,
         "loss": loss_value,
         "device_status": status,
         "step_tflops_per_gpu": tf_step,
@@ -375,10 +436,14 @@ def run_ours(args) -> None:
                      "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
                      "algorithmic_bytes_per_launch": (n * h + v_loc * h) * 2 + (v_loc + 255) // 256 * 3 * n * 4},
         "e2e": {"value": n / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + t_host.numel() * t_host.element_size(),
-                "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
+                "note": "bytes per rank; at N > 1 each rank copies its row slice and one all-gather over NVLink "
+                        "rebuilds the batch" if world > 1 else "whole batch from pinned host memory"},
         "gpu_launches": int(launches),
-        "clocks": clocks,
+        "clocks": dict(clocks, reasons=reasons),
+        "cycles": {"ms_x_mhz": max(a * b for a, b in per_rank), "sm_mhz_per_rank": [b for _, b in per_rank],
+                   "ms_per_step_per_rank": [a for a, _ in per_rank],
+                   "note": "ms_per_step x median SM MHz, max over ranks: step cost in thousands of SM cycles"},
     }
     if base is not None:
         line["cpu_baseline"] = base
@@ -396,6 +461,8 @@ def main() -> None:
     ap.add_argument("--workload", default="llama3-8b",
                     help="llama3-8b (headline), gpt2-small, large-vocab, 14b-class, sweep-<rows>")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--preheat-s", type=float, default=2.0,
+                    help="seconds of untimed steps before the timed region, so that it runs at the sustained clock")
     ap.add_argument("--forward-only", action="store_true",
                     help="time the forward alone with reduction='none' (per-token loss), 2 N H V FLOPs per step")
     args = ap.parse_args()

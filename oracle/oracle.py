@@ -360,3 +360,34 @@ def merge_stats(stats: torch.Tensor, target: torch.Tensor, *, reduction: str = "
     else:
         loss = nll.sum() / valid.sum()
     return {"loss": loss, "lse": lse}
+
+
+def shard_backward_chunked(hidden: torch.Tensor, weight_shard: torch.Tensor, target: torch.Tensor, vocab_start: int,
+                           lse: torch.Tensor, scale: torch.Tensor, chunk_rows: int = 1024) -> dict:
+    """What ONE rank of a vocabulary-parallel backward contributes, in fp32 with O(chunk_rows x V_local) memory:
+    ``G = (exp(z_local - lse_global) - onehot) * scale`` over the shard's columns, the partial ``dx = G @ W_r``
+    (to be summed over ranks) and the local ``dw = G^T @ X``. ``scale`` is the per-row factor (0 for ignored
+    rows). Also returns the shard's ``[3, N]`` statistics as ``shard_stats`` defines them."""
+    h32 = hidden.detach().float().reshape(-1, hidden.shape[-1])
+    w32 = weight_shard.detach().float()
+    t = target.reshape(-1).long() - vocab_start
+    n = h32.shape[0]
+    dx = torch.empty_like(h32)
+    dw = torch.zeros_like(w32)
+    stats = torch.empty((3, n), dtype=torch.float32, device=h32.device)
+    for r0 in range(0, n, chunk_rows):
+        r1 = min(n, r0 + chunk_rows)
+        z = h32[r0:r1] @ w32.T
+        tc = t[r0:r1]
+        inside = (tc >= 0) & (tc < z.shape[1])
+        safe = torch.where(inside, tc, torch.zeros_like(tc))
+        m = z.max(dim=1).values
+        stats[0, r0:r1] = m
+        stats[1, r0:r1] = torch.exp(z - m[:, None]).sum(dim=1)
+        stats[2, r0:r1] = torch.where(inside, z.gather(1, safe[:, None])[:, 0], torch.full_like(m, -math.inf))
+        g = torch.exp(z - lse[r0:r1, None].float())
+        g[torch.arange(r1 - r0, device=g.device)[inside], safe[inside]] -= 1.0
+        g *= scale[r0:r1, None].float()
+        dx[r0:r1] = g @ w32
+        dw += g.T @ h32[r0:r1]
+    return {"dx": dx, "dw": dw, "stats": stats}

@@ -201,3 +201,27 @@ def test_expression_is_within_the_reference_tolerance_of_its_kernels(name):
     torch.testing.assert_close(ref["loss"], exp["loss"], rtol=2e-2, atol=2e-3)
     torch.testing.assert_close(ref["dx"].float(), exp["dx"].to(dtype).float().reshape(ref["dx"].shape), rtol=rtol, atol=atol)
     torch.testing.assert_close(ref["dw"].float(), exp["dw"].to(dtype).float(), rtol=rtol, atol=atol)
+
+
+def test_sharded_backward_of_all_ranks_adds_up_to_the_unsharded_gradients():
+    """The per-rank oracle used for the full-size shard test: partial dX summed over the shards, the local dW
+    blocks side by side and the merged statistics reproduce the unsharded expression."""
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(70, 48, generator=g).bfloat16()
+    w = (torch.randn(403, 48, generator=g) * 0.2).bfloat16()
+    t = torch.randint(0, 403, (70,), generator=g)
+    t[::9] = -100
+    full = oracle.expression(x, w, t, reduction="sum", grad_out=torch.tensor(0.25))
+    scale = torch.where(t != -100, torch.tensor(0.25), torch.tensor(0.0))
+    dx = torch.zeros(70, 48)
+    stats, dws = [], []
+    for start, end in [(0, 101), (101, 202), (202, 303), (303, 403)]:
+        part = oracle.shard_backward_chunked(x, w[start:end], t, start, full["lse"], scale, chunk_rows=32)
+        dx += part["dx"]
+        dws.append(part["dw"])
+        stats.append(part["stats"])
+        torch.testing.assert_close(part["stats"], oracle.shard_stats(x, w[start:end], t, start))
+    torch.testing.assert_close(dx, full["dx"], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(torch.cat(dws), full["dw"], rtol=1e-5, atol=1e-6)
+    merged = oracle.merge_stats(torch.stack(stats), t, reduction="sum")
+    torch.testing.assert_close(merged["loss"], full["loss"], rtol=1e-5, atol=1e-5)
