@@ -63,6 +63,8 @@ SIGNATURES = {
     "lce_rmsnorm_plan": (c_int, [c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "lce_rmsnorm_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, ctypes.c_float, c_int, c_void_p, c_size_t, c_void_p]),
+    "lce_set_tuning": (None, [c_int, c_int, c_int]),
+    "lce_debug_wait_test": (c_int, [ctypes.c_ulonglong, c_uint]),
     "lce_debug_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                c_uint, c_void_p]),
 }

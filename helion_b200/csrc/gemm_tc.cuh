@@ -15,7 +15,13 @@
 //   warps 2-5   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
 // Pipelines: STAGES-deep smem ring (full/empty mbarriers) between producer and issuer, and two
 // accumulator buffers in TMEM (tmem_full/tmem_empty) so the epilogue of tile i overlaps the main
-// loop of tile i+1. Tiles are dealt round-robin to a persistent grid.
+// loop of tile i+1. Tiles are dealt to a persistent grid either round-robin (static) or, for launches of
+// many waves, from a global counter (dynamic): the producer of each CTA (pair) draws the index of its next
+// tile with an atomicAdd one tile ahead and hands it to the other roles through a small ring in shared
+// memory. Dynamic dealing keeps the set of tiles in flight a contiguous window of the tile order, whatever
+// the speed of the individual SMs; with the static deal slower CTAs fall behind by whole waves over a long
+// launch, the operand panels they share with their neighbours have left L2 by the time they need them, and
+// DRAM traffic grows to several times the algorithmic bytes.
 //
 // Two variants, selected by CG:
 //   CG = 1  one CTA per tile: tcgen05.mma.cta_group::1, M = 128. 48 KB per stage (A 16 + B 32).
@@ -47,6 +53,8 @@ constexpr int kGemmThreads = 192;
 constexpr int kDevErrProducerTimeout = 101;
 constexpr int kDevErrMmaTimeout = 102;
 constexpr int kDevErrEpilogueTimeout = 103;
+constexpr int kDevErrSchedTimeout = 104;
+constexpr int kSchedSlots = 4;  // depth of the tile-index ring of the dynamic scheduler
 
 struct TileCtx {
     int m_tile;       // 128-row tile index
@@ -110,7 +118,7 @@ template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                int m_tiles, int n_tiles, int k_blocks, int k_splits, int raster, int l2_hints,
-               const typename Epi::Params ep, int* __restrict__ status) {
+               const typename Epi::Params ep, int* __restrict__ status, int* __restrict__ sched_counter) {
     using S = GemmSmem<BN, STAGES, CG>;
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(BN % (64 * CG) == 0 && BN >= 64 && BN <= 256, "tile width");
@@ -132,7 +140,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile uint32_t* tmem_ptr_smem =
         reinterpret_cast<volatile uint32_t*>(gen_bar_base + 8 * (2 * STAGES + 5));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_bar_base + 8 * (2 * STAGES + 5) + 4);
-    static_assert(8 * (2 * STAGES + 6) <= S::kBarrierBytes, "barrier block too small");
+    // dynamic scheduler: sched_full[kSchedSlots] | sched_empty[kSchedSlots] | tile index per slot
+    auto sfull_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 6 + q); };
+    auto sempty_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 6 + kSchedSlots + q); };
+    const uint32_t sched_tiles = bar_base + 8u * (2 * STAGES + 6 + 2 * kSchedSlots);
+    volatile int* sched_tile_gen = reinterpret_cast<volatile int*>(gen_bar_base + 8 * (2 * STAGES + 6 + 2 * kSchedSlots));
+    static_assert(8 * (2 * STAGES + 6 + 2 * kSchedSlots) + 4 * kSchedSlots <= S::kBarrierBytes, "barrier block too small");
+    const bool dyn = sched_counter != nullptr;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -154,6 +168,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ptx::mbar_init(tempty_bar(b), 4 * CG);  // one arrival per epilogue warp of the group
         }
         ptx::mbar_init(drain_bar, 1);
+        for (int q = 0; q < kSchedSlots; ++q) {
+            ptx::mbar_init(sfull_bar(q), 1);  // the leader's producer publishes
+            // readers of a slot: MMA issuer, the epilogue warps of the group, the peer's producer
+            ptx::mbar_init(sempty_bar(q), 1 + 4 * CG + (CG - 1));
+        }
         *abort_flag = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmA);
@@ -174,6 +193,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
+    // Reader side of the tile deal: the work item that follows the `seq`-th one this CTA handled.
+    // Static deal: the next one round-robin. Dynamic deal: what the leader's producer put into ring slot
+    // seq % kSchedSlots (a value >= total_work ends the loop); the slot is released on the leader's barrier.
+    auto next_work = [&](int work, uint32_t seq, bool release, bool& ok) -> int {
+        if (!dyn) return work + unit_step;
+        const uint32_t q = seq % kSchedSlots, par = (seq / kSchedSlots) & 1u;
+        if (!ptx::mbar_wait_cluster(sfull_bar(q), par, abort_flag)) {
+            ok = false;
+            return total_work;
+        }
+        const int nxt = sched_tile_gen[q];
+        if (release) {
+            if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(sempty_bar(q), 0));
+            else ptx::mbar_arrive(sempty_bar(q));
+        }
+        return nxt;
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
@@ -183,7 +220,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // l2_hints: eviction priority of operand A in bits 0-1, of operand B in bits 2-3
             const uint64_t policy_a = ptx::make_l2_policy(l2_hints & 3);
             const uint64_t policy_b = ptx::make_l2_policy((l2_hints >> 2) & 3);
-            for (int work = unit0; work < total_work && ok; work += unit_step) {
+            const uint32_t announce_extra = ptx::g_debug_announce_extra;  // test hook: 0 outside the wait-expiry test
+            // dynamic deal (leader only): `nxt` is the work item after the current one, drawn one tile ahead
+            int nxt = total_work, drawn = total_work;
+            uint32_t seq = 0;
+            if (dyn && cta_rank == 0) nxt = unit_step + atomicAdd(sched_counter, 1);
+            for (int work = unit0; work < total_work && ok;) {
+                if (dyn && cta_rank == 0) {
+                    // publish the successor of this tile to the other roles (and to the peer CTA), then draw
+                    // the one after it: its value is not needed before the next iteration
+                    const uint32_t q = seq % kSchedSlots, par = (seq / kSchedSlots) & 1u;
+                    if (!ptx::mbar_wait_cluster(sempty_bar(q), par ^ 1u, abort_flag)) {
+                        atomicCAS(status, 0, kDevErrSchedTimeout);
+                        ok = false;
+                        break;
+                    }
+                    sched_tile_gen[q] = nxt;
+                    if constexpr (kPair) {
+                        ptx::st_shared_cluster_u32(ptx::map_to_cta(sched_tiles + 4u * q, 1), static_cast<uint32_t>(nxt));
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(sfull_bar(q), 1));
+                    }
+                    ptx::mbar_arrive(sfull_bar(q));
+                    drawn = nxt < total_work ? unit_step + atomicAdd(sched_counter, 1) : total_work;
+                }
                 int m_unit, n_tile;
                 tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
                 const int kb_begin = (work / total_units) * kb_per_slice;
@@ -207,7 +266,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         else ptx::tma_load_2d_hint(dst, tm, fb, x, y, policy);
                     };
                     // bytes of the whole group's copies for this stage, announced by the leader only
-                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes * CG);
+                    if (cta_rank == 0)
+                        ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes * CG + (issued == 0 ? announce_extra : 0u));
                     if constexpr (!A_MN) {
                         load(sa, &tmA, kb * kBK, m_tile * kBM);
                     } else {
@@ -224,6 +284,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     ++issued;
                 }
+                if (!ok) break;
+                if (dyn && cta_rank == 0) {
+                    work = nxt;
+                    nxt = drawn;
+                } else {
+                    work = next_work(work, seq, true, ok);
+                }
+                ++seq;
             }
             if (!ok || *abort_flag) {
                 // Unwinding: give every copy already in flight time to land before the CTA retires.
@@ -251,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t consumed = 0;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int work = unit0; work < total_work && ok; work += unit_step, ++local_tile) {
+            for (int work = unit0; work < total_work && ok; ++local_tile) {
                 const int kb_begin = (work / total_units) * kb_per_slice;
                 const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
                 const uint32_t buf = local_tile & 1u;
@@ -294,6 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (ok) {  // accumulator complete
                     if constexpr (kPair) ptx::umma_commit_pair(tfull_bar(buf), 3);
                     else ptx::umma_commit(tfull_bar(buf));
+                    work = next_work(work, local_tile, true, ok);
                 }
             }
             if (!ok || *abort_flag) {
@@ -311,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t local_tile = 0;
         bool ok = true;
         typename Epi::State st;
-        for (int work = unit0; work < total_work && ok; work += unit_step, ++local_tile) {
+        for (int work = unit0; work < total_work && ok; ++local_tile) {
             int m_unit, n_tile;
             tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
             const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
@@ -341,6 +410,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 else ptx::mbar_arrive(tempty_bar(buf));
             }
             Epi::end(st, ep, tc);
+            // every lane reads the next work item; one lane releases the ring slot for the warp
+            const int following = next_work(work, local_tile, false, ok);
+            if (dyn && ok) {
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t q = local_tile % kSchedSlots;
+                    if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(sempty_bar(q), 0));
+                    else ptx::mbar_arrive(sempty_bar(q));
+                }
+            }
+            work = following;
         }
         if (!ok && lane == 0) atomicCAS(status, 0, kDevErrEpilogueTimeout);
     }

@@ -137,19 +137,32 @@ struct Mat {
     long long rows, cols, pitch_elems;
 };
 
+// Tuning knobs of the tcgen05 launches (environment at load time, lce_set_tuning at run time):
+//   band_mb     size of the operand band the tile order keeps resident in L2 (HELION_B200_BAND_MB)
+//   hint_mode   L2 eviction hints: 0 none, 1 resident operand evict_last + streaming evict_first,
+//               2 evict_last only (HELION_B200_L2_HINTS)
+//   dyn_waves   launches of at least this many waves of tiles deal their tiles dynamically, when the caller's
+//               workspace has room for the counter; 0 = never (HELION_B200_DYN_WAVES)
+struct Tuning {
+    std::atomic<int> band_mb, hint_mode, dyn_waves;
+    Tuning() {
+        const char* e = getenv("HELION_B200_BAND_MB");
+        band_mb = (e && atoi(e) > 0) ? atoi(e) : 32;
+        e = getenv("HELION_B200_L2_HINTS");
+        hint_mode = e ? atoi(e) : 2;
+        e = getenv("HELION_B200_DYN_WAVES");
+        dyn_waves = e ? atoi(e) : 3;
+    }
+};
+Tuning g_tuning;
+
 template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-                 int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream) {
+                 int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream, int* sched) {
     // Band the tile order so that the panels which co-running CTAs do NOT share stay resident in L2:
     // about 32 MB of them (the two L2 partitions of 63 MB each also hold the streaming operand).
-    static const long long kBandBytes = [] {  // HELION_B200_BAND_MB overrides (tuning knob)
-        const char* e = getenv("HELION_B200_BAND_MB");
-        return (e && atoll(e) > 0 ? atoll(e) : 32ll) << 20;
-    }();
-    static const int kHintMode = [] {  // 0 none, 1 resident operand evict_last + streaming evict_first, 2 evict_last only
-        const char* e = getenv("HELION_B200_L2_HINTS");
-        return e ? atoi(e) : 2;
-    }();
+    const long long kBandBytes = static_cast<long long>(g_tuning.band_mb.load(std::memory_order_relaxed)) << 20;
+    const int kHintMode = g_tuning.hint_mode.load(std::memory_order_relaxed);
     constexpr int kStages = CG == 2 ? kStages2 : kStages1;
     const int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
     CUtensorMap tma, tmb;
@@ -204,9 +217,13 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
         long long wb = kBandBytes / (static_cast<long long>(kBN) * K * 2);
         raster = -static_cast<int>(wb < 1 ? 1 : (wb > n_tiles ? n_tiles : wb));
     }
+    // Long launches deal their tiles from a counter in the caller's workspace, zeroed in stream order here.
+    const int dyn_waves = g_tuning.dyn_waves.load(std::memory_order_relaxed);
+    int* counter = (sched != nullptr && dyn_waves > 0 && work >= dyn_waves * slots) ? sched : nullptr;
+    if (counter != nullptr && cudaMemsetAsync(counter, 0, sizeof(int), stream) != cudaSuccess) return LCE_ERR_CUDA;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
-                                               raster, l2_hints, ep, d.status_ptr);
+                                               raster, l2_hints, ep, d.status_ptr, counter);
     LCE_COUNT_LAUNCH();
     return err == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
@@ -225,14 +242,16 @@ inline int cta_group_of(unsigned flags) { return (flags & LCE_FLAG_ONE_CTA) ? 1 
 struct Path {
     bool use_tc;  // tcgen05 GEMM core (else the CUDA-core one)
     int cg;       // cta group asked for: 2 = CTA pairs, 1 = single CTAs
+    int* sched = nullptr;  // 4 bytes of the call's workspace for the dynamic tile deal, or nullptr
 };
 
 template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc(const DeviceInfo& d, int cg, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1) {
+              int m_fastest, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1,
+              int* sched = nullptr) {
     if (use_pair(M, cg))
-        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
-    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream);
+        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched);
+    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched);
 }
 
 // The same for the CUDA-core GEMM (128 x 128 tiles, two CTAs per SM worth of work items).
@@ -368,7 +387,7 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiStats>(d, cg, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream);
+            rc = launch_tc<false, false, kBf16, EpiStats>(d, cg, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream, 1, path.sched);
         } else {
             rc = LCE_ERR_ARG;
         }
@@ -407,7 +426,7 @@ int greedy_head_impl(const DeviceInfo& d, const Path& path, const void* x, const
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiTop1>(d, cg, a, b, N, V, H, 1, ep, stream);
+            rc = launch_tc<false, false, kBf16, EpiTop1>(d, cg, a, b, N, V, H, 1, ep, stream, 1, path.sched);
         } else {
             rc = LCE_ERR_ARG;
         }
@@ -547,7 +566,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 const Mat a{xp + r0 * H, nr, H, H}, b{wp + c0 * H, nc, H, H};
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<false, false, kBf16, EpiGrad<T>>(d, cg, a, b, nr, nc, H, 1, ep, stream);
+                        rc = launch_tc<false, false, kBf16, EpiGrad<T>>(d, cg, a, b, nr, nc, H, 1, ep, stream, 1, path.sched);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiGrad<T>>(d, a, false, b, false, nr, nc, H, ep, stream);
@@ -582,7 +601,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 if (splits > 1) ep.mode = kStoreSlice;
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, cg, gm, b, nr, H, nc, 0, ep, stream, splits);
+                        rc = launch_tc<false, true, kBf16, EpiStore<TDx>>(d, cg, gm, b, nr, H, nc, 0, ep, stream, splits, path.sched);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<TDx>>(d, gm, false, b, true, nr, H, nc, ep, stream, splits);
@@ -625,7 +644,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 }
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
-                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, cg, gm, b, nc, H, nr, 0, ep, stream, wsplits);
+                        rc = launch_tc<true, true, kBf16, EpiStore<T>>(d, cg, gm, b, nc, H, nr, 0, ep, stream, wsplits, path.sched);
                     else rc = LCE_ERR_ARG;
                 } else {
                     rc = launch_simt<T, EpiStore<T>>(d, gm, true, b, true, nc, H, nr, ep, stream, wsplits);
@@ -658,6 +677,12 @@ extern "C" {
 int lce_version(void) { return LCE_VERSION; }
 
 unsigned long long lce_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void lce_set_tuning(int band_mb, int l2_hint_mode, int dyn_waves) {
+    if (band_mb > 0) g_tuning.band_mb.store(band_mb, std::memory_order_relaxed);
+    if (l2_hint_mode >= 0) g_tuning.hint_mode.store(l2_hint_mode, std::memory_order_relaxed);
+    if (dyn_waves >= 0) g_tuning.dyn_waves.store(dyn_waves, std::memory_order_relaxed);
+}
 
 const char* lce_strerror(int code) {
     switch (code) {
@@ -711,13 +736,16 @@ int lce_forward_stats(const void* x, const void* w, const void* target, int targ
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     FwdOutputs fo;
     fo.stats = stats;
+    const size_t sched_off = align_up(fwd_layout(N, V, use_tc).bytes, 256);  // the slack lce_forward_workspace_bytes adds
+    const Path path{use_tc, cta_group_of(flags),
+                    ws_bytes >= sched_off + sizeof(int) ? reinterpret_cast<int*>(static_cast<char*>(ws) + sched_off) : nullptr};
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return forward_stats_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<__nv_bfloat16>(*d, path, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         case LCE_DTYPE_F16:
-            return forward_stats_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<__half>(*d, path, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
         default:
-            return forward_stats_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
+            return forward_stats_impl<float>(*d, path, x, w, target, target_is_i64, N, H, V, vocab_start, fo, ws, s);
     }
 }
 
@@ -735,13 +763,16 @@ int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t 
     if (ws_bytes < fwd_layout(N, V, use_tc).bytes) return LCE_ERR_WS_TOO_SMALL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     long long* tok = reinterpret_cast<long long*>(token);
+    const size_t sched_off = align_up(fwd_layout(N, V, use_tc).bytes, 256);
+    const Path path{use_tc, cta_group_of(flags),
+                    ws_bytes >= sched_off + sizeof(int) ? reinterpret_cast<int*>(static_cast<char*>(ws) + sched_off) : nullptr};
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            return greedy_head_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<__nv_bfloat16>(*d, path, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
         case LCE_DTYPE_F16:
-            return greedy_head_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<__half>(*d, path, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
         default:
-            return greedy_head_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+            return greedy_head_impl<float>(*d, path, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
     }
 }
 
@@ -806,15 +837,18 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
     fo.lse = lse;
     fo.loss_rows = reduction == LCE_REDUCTION_NONE ? loss : reinterpret_cast<float*>(static_cast<char*>(ws) + partial_bytes);
     fo.ignore_index = ignore_index;
+    const size_t sched_off = partial_bytes + align_up(static_cast<size_t>(N) * sizeof(float), 256);
+    const Path path{use_tc, cta_group_of(flags),
+                    ws_bytes >= sched_off + sizeof(int) ? reinterpret_cast<int*>(static_cast<char*>(ws) + sched_off) : nullptr};
     switch (dtype) {
         case LCE_DTYPE_BF16:
-            rc = forward_stats_impl<__nv_bfloat16>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<__nv_bfloat16>(*d, path, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
             break;
         case LCE_DTYPE_F16:
-            rc = forward_stats_impl<__half>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<__half>(*d, path, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
             break;
         default:
-            rc = forward_stats_impl<float>(*d, Path{use_tc, cta_group_of(flags)}, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
+            rc = forward_stats_impl<float>(*d, path, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
     }
     if (rc) return rc;
     if (reduction != LCE_REDUCTION_NONE || valid_count) {
@@ -901,10 +935,12 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     LCE_COUNT_LAUNCH();
     if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
+    // the 256-byte head of the workspace holds the valid-row count (float 0) and the tile-deal counter (byte 128)
+    const Path path{use_tc, cta_group_of(flags), reinterpret_cast<int*>(wsc + p.off_count + 128)};
 #define LCE_BWD(T)                                                                                          \
-    (dx32 ? backward_impl<T, float>(*d, Path{use_tc, cta_group_of(flags)}, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
+    (dx32 ? backward_impl<T, float>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
                                     dx, dw, wsc, flags, dx_events, scatter, s)                              \
-          : backward_impl<T, T>(*d, Path{use_tc, cta_group_of(flags)}, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
+          : backward_impl<T, T>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
                                 dw, wsc, flags, dx_events, nullptr, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
@@ -912,6 +948,18 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
         default: return LCE_BWD(float);
     }
 #undef LCE_BWD
+}
+
+int lce_debug_wait_test(unsigned long long limit_ns, unsigned announce_extra_bytes) {
+    DeviceInfo* d;
+    int rc = device_info(&d);
+    if (rc) return rc;
+    const unsigned long long limit = limit_ns ? limit_ns : LCE_WAIT_LIMIT_NS;
+    if (cudaDeviceSynchronize() != cudaSuccess) return LCE_ERR_CUDA;
+    if (cudaMemcpyToSymbol(ptx::g_wait_limit_ns, &limit, sizeof(limit)) != cudaSuccess) return LCE_ERR_CUDA;
+    if (cudaMemcpyToSymbol(ptx::g_debug_announce_extra, &announce_extra_bytes, sizeof(unsigned)) != cudaSuccess)
+        return LCE_ERR_CUDA;
+    return LCE_OK;
 }
 
 int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,

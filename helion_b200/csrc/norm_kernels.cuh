@@ -289,7 +289,8 @@ __device__ __forceinline__ void rms_ring_issue(RmsRing& ring, unsigned char* dat
     const int nr = n_rows - row0 < ROWS ? static_cast<int>(n_rows - row0) : ROWS;
     const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
     const uint32_t bar = ptx::smem_u32(&ring.full[s]);
-    ptx::mbar_arrive_expect_tx(bar, nr * row_bytes * NS);
+    // g_debug_announce_extra is 0 except in the wait-expiry test (a read of a cached word per row group)
+    ptx::mbar_arrive_expect_tx(bar, nr * row_bytes * NS + ptx::g_debug_announce_extra);
     unsigned char* dst = data + static_cast<size_t>(s) * (ROWS * NS * row_bytes);
 #pragma unroll
     for (int n = 0; n < NS; ++n)

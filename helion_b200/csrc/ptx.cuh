@@ -90,9 +90,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same with acquire semantics at cluster scope: for a barrier whose arrival publishes data that
+// the peer CTA of a cluster wrote into this CTA's shared memory.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred P;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, P;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 #ifndef LCE_WAIT_LIMIT_NS
 #define LCE_WAIT_LIMIT_NS 2000000000ull  // 2 s: three orders of magnitude above any legitimate wait
 #endif
+
+// The limit every bounded wait uses, in nanoseconds of %globaltimer. A variable rather than a constant so
+// that a test can shorten it to a few milliseconds and watch a wait run out (read only on the slow path).
+__device__ unsigned long long g_wait_limit_ns = LCE_WAIT_LIMIT_NS;
+
+// Test hook, 0 in normal operation: a producer announces this many bytes MORE on its first full-barrier
+// than its copies deliver. The copies all land, the barrier never completes, and the consumer's bounded
+// wait runs out: the one way to exercise the unwinding paths without anything left in flight.
+__device__ unsigned int g_debug_announce_extra = 0;
 
 // Bounded wait on an mbarrier phase. `abort_flag` lives in shared memory and is shared by all
 // roles of the CTA: once any role gives up, every other role's next wait returns false at once.
@@ -105,7 +130,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > LCE_WAIT_LIMIT_NS) {
+            else if (now - t0 > g_wait_limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    uint64_t t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > g_wait_limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
@@ -302,6 +344,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 // Arrival on a barrier that may live in the peer CTA (address from map_to_cta).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// 32-bit store into the shared memory of any CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
 }
 
 // TMA load whose completion is counted on a barrier of either CTA of the pair (no multicast:

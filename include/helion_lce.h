@@ -279,6 +279,22 @@ int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, cons
  * for 16-bit inputs. a_mn_major = 0: a is [M, K] row-major; 1: a is [K, M] row-major. Same for b
  * with N. No counterpart in the reference; exists so the operand-layout handling can be tested
  * in isolation. */
+/* Tuning knobs of the tcgen05 launches, process-wide, for measurements: band_mb = MiB of operand panels the
+ * tile order keeps resident in L2 (default 32), l2_hint_mode = 0 no eviction hints, 1 resident operand
+ * evict_last + streaming operand evict_first, 2 evict_last only (default), dyn_waves = launches of at least
+ * this many waves of tiles draw their tiles from a counter instead of round-robin (default 3, 0 = never).
+ * A value that is out of range (band_mb <= 0, the others < 0) leaves that knob as it is. Results do not depend
+ * on any of them. Test infrastructure like lce_debug_gemm. */
+void lce_set_tuning(int band_mb, int l2_hint_mode, int dyn_waves);
+
+/* Wait-expiry test hook (test infrastructure): every wait inside the kernels is bounded (2 s by default) and
+ * unwinds with a code in the device status word when the bound is hit. This sets, on the current device, the
+ * bound to limit_ns (0 = back to the default) and makes the producers announce announce_extra_bytes more on
+ * a barrier than their copies deliver (0 = normal operation), so that a test can watch the bound being hit
+ * with nothing left in flight: all copies land, no barrier completes, nothing traps or faults, and the
+ * kernel returns. Synchronises the device. Always call it again with (0, 0) afterwards. */
+int lce_debug_wait_test(unsigned long long limit_ns, unsigned announce_extra_bytes);
+
 int lce_debug_gemm(const void* a, const void* b, float* out, int64_t M, int64_t N, int64_t K,
                    int a_mn_major, int b_mn_major, int dtype, unsigned flags, void* stream);
 
