@@ -1,8 +1,12 @@
-"""Decode-step timings of the greedy head on the Llama-3-8B LM head (4096 x 128256, bf16).
+"""Decode-step timings of the greedy head and the top-k sampling head on the Llama-3-8B LM head
+(4096 x 128256, bf16).
 
 A decode step reads the whole weight once (V*H*elem bytes; the batch is tiny), so the yardstick is HBM
 bandwidth. Providers: ``helion_b200`` (``greedy_head``: argmax and log-probability, logits never written),
-``torch_eager`` (``hidden @ weight.T`` in bf16, then argmax / logsumexp of the materialised logits),
+``helion_b200_topk50`` (``topk_head`` with k = 50: the candidates and the logsumexp that temperature / top-k /
+nucleus sampling needs), ``torch_eager`` (``hidden @ weight.T`` in bf16, then argmax / logsumexp of the
+materialised logits), ``torch_eager_topk50`` (the same product, then ``torch.topk(logits.float(), 50)`` and
+``logsumexp``, as the reference's ``sample_next_token`` does, examples/common.py:284-289),
 ``reference_decode`` (what the reference's model does per step, examples/common.py:127-131:
 ``matmul(hidden, lm_head.T.contiguous())`` - the transpose copy included - then argmax; torch.matmul stands in
 for tritium.matmul so that only the extra copy and the logits write are being compared).
@@ -31,7 +35,7 @@ def main() -> None:
     ap.add_argument("--rows", default="1,16,128,1024")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
-    ap.add_argument("--providers", default="helion_b200,torch_eager,reference_decode")
+    ap.add_argument("--providers", default="helion_b200,helion_b200_topk50,torch_eager,torch_eager_topk50,reference_decode")
     args = ap.parse_args()
     require_cuda()
     peaks = ROOT / "MEASURED_PEAKS.json"
@@ -46,8 +50,13 @@ def main() -> None:
             z = hidden @ weight.T
             return z.argmax(dim=-1), torch.logsumexp(z.float(), dim=-1)
 
+        def eager_topk():
+            z = (hidden @ weight.T).float()
+            return torch.topk(z, 50, dim=-1), torch.logsumexp(z, dim=-1)
+
         for provider, fn in (("helion_b200", lambda: helion_b200.greedy_head(hidden, weight)),
-                             ("torch_eager", eager), ("reference_decode", lambda: (hidden @ weight.T.contiguous()).argmax(dim=-1))):  # the transpose copy per step
+                             ("helion_b200_topk50", lambda: helion_b200.topk_head(hidden, weight, 50)),
+                             ("torch_eager", eager), ("torch_eager_topk50", eager_topk), ("reference_decode", lambda: (hidden @ weight.T.contiguous()).argmax(dim=-1))):  # the transpose copy per step
             if provider not in args.providers.split(","):
                 continue
             ms = bench_ms(fn)

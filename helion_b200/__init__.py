@@ -6,7 +6,7 @@ Importing this package needs no GPU; calling an op needs libhelion_lce.so (built
 """
 
 from .ce_ops import cross_entropy, cross_entropy_backward
-from .decode_ops import greedy_head
+from .decode_ops import greedy_head, sample_head, topk_head
 from .install import install, uninstall
 from .matmul_ops import matmul, matmul_vec
 from .norm_ops import residual_rmsnorm, rmsnorm, rmsnorm_backward
@@ -28,5 +28,7 @@ __all__ = [
     "residual_rmsnorm",
     "rmsnorm",
     "rmsnorm_backward",
+    "sample_head",
+    "topk_head",
     "uninstall",
 ]

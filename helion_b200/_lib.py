@@ -57,6 +57,9 @@ SIGNATURES = {
     "lce_sumsq": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "lce_greedy_head": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
+    "lce_topk_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
+    "lce_topk_head": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, ctypes.c_float,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_uint, c_void_p]),
     "lce_rmsnorm_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                     ctypes.c_float, c_int, c_void_p]),
     "lce_rmsnorm_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int]),

@@ -192,6 +192,95 @@ struct EpiTop1 {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Sampling head: per (vocab tile, row) the kTileTop largest SCALED logits y = z * scale (scale = 1 /
+// temperature) with their columns, sorted (larger first; on equal values the lower column first), and the
+// tile's max / sum exp(y - max). Record layout, kTopRecord floats per (tile, row), component-major like
+// EpiStats:   0 max   1 sum-exp   2 .. 2+kTileTop-1 values   2+kTileTop .. columns (int bits, local).
+// Slots beyond the tile's valid columns hold -inf / column -1. A per-row merge (merge_topk_kernel) selects
+// the k best of all tiles; a tile may hold more than kTileTop of them, which the merge detects (the
+// tile's weakest kept entry still outranks the k-th) and repairs by recomputing that tile's logits.
+// No counterpart in the reference: its decode step materialises all V logits and calls torch.topk /
+// torch.sort on them (examples/common.py:288-301, 380-384).
+// ---------------------------------------------------------------------------------------------
+constexpr int kTileTop = 8;
+constexpr int kTopRecord = 2 + 2 * kTileTop;
+
+struct EpiTopK {
+    struct Params {
+        int rows;   // valid rows
+        int vocab;  // valid columns (local shard width)
+        float scale;
+        float* partial;
+        long long row_stride;
+    };
+    struct State {
+        float m, s;
+        float val[kTileTop];
+        int col[kTileTop];
+        int row;
+    };
+    static __device__ __forceinline__ void begin(State& st, const Params&, const TileCtx& tc) {
+        st.row = tc.m_tile * kBM + tc.row_in_tile;
+        st.m = -INFINITY;
+        st.s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kTileTop; ++i) {
+            st.val[i] = -INFINITY;
+            st.col[i] = -1;
+        }
+    }
+    static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
+                                                 int col0, float (&v)[32]) {
+        const int gcol0 = tc.n_tile * tc.bn + col0;
+        if (gcol0 >= p.vocab) return;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (gcol0 + j < p.vocab) ? v[j] * p.scale : -INFINITY;
+        float cm = v[0];
+#pragma unroll
+        for (int j = 1; j < 32; ++j) cm = fmaxf(cm, v[j]);
+        if (cm > st.val[kTileTop - 1]) {  // something in this chunk enters the list
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (v[j] > st.val[kTileTop - 1]) {  // strict: of equal values the earlier column stays
+                    st.val[kTileTop - 1] = v[j];
+                    st.col[kTileTop - 1] = gcol0 + j;
+#pragma unroll
+                    for (int i = kTileTop - 2; i >= 0; --i) {
+                        if (st.val[i + 1] > st.val[i]) {
+                            const float tv = st.val[i];
+                            st.val[i] = st.val[i + 1];
+                            st.val[i + 1] = tv;
+                            const int tcl = st.col[i];
+                            st.col[i] = st.col[i + 1];
+                            st.col[i + 1] = tcl;
+                        }
+                    }
+                }
+            }
+        }
+        const float nm = fmaxf(st.m, cm);
+        const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += ptx::ex2(fmaf(v[j], kLog2e, -nm2));
+        st.s = st.s * ptx::ex2(fmaf(st.m, kLog2e, -nm2)) + acc;
+        st.m = nm;
+    }
+    static __device__ __forceinline__ void end(State& st, const Params& p, const TileCtx& tc) {
+        if (st.row < p.rows) {
+            float* base = p.partial + static_cast<long long>(tc.n_tile) * kTopRecord * p.row_stride + st.row;
+            base[0] = st.m;
+            base[p.row_stride] = st.s;
+#pragma unroll
+            for (int i = 0; i < kTileTop; ++i) {
+                base[(2 + i) * p.row_stride] = st.val[i];
+                base[(2 + kTileTop + i) * p.row_stride] = __int_as_float(st.col[i]);
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
 // Backward step 1: recompute a logits tile and turn it into the logit gradient
 //   G[row, col] = (exp(z - lse[row]) - [col == target[row]]) * rowscale[row]
 // rounded to the input dtype (the reference rounds G the same way before its two GEMMs,

@@ -16,6 +16,7 @@
 #include "norm_kernels.cuh"
 #include "optim_kernels.cuh"
 #include "row_kernels.cuh"
+#include "topk_kernels.cuh"
 
 namespace lce {
 
@@ -441,6 +442,46 @@ int greedy_head_impl(const DeviceInfo& d, const Path& path, const void* x, const
     return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
+// Sampling head: the forward GEMM with the top-candidates epilogue, then the per-row selection.
+size_t topk_partial_bytes(long long N, long long V, bool use_tc) {
+    const FwdLayout l = fwd_layout(N, V, use_tc);
+    return static_cast<size_t>(l.n_tiles) * kTopRecord * l.row_stride * sizeof(float);
+}
+
+template <class T>
+int topk_head_impl(const DeviceInfo& d, const Path& path, const void* x, const void* w, long long N, long long H,
+                   long long V, long long vocab_start, int K, float scale, float* top_val, long long* top_idx,
+                   float* lse, void* ws, cudaStream_t stream) {
+    const bool use_tc = path.use_tc;
+    const int cg = path.cg;
+    const FwdLayout l = fwd_layout(N, V, use_tc);
+    EpiTopK::Params ep;
+    ep.rows = static_cast<int>(N);
+    ep.vocab = static_cast<int>(V);
+    ep.scale = scale;
+    ep.partial = static_cast<float*>(ws);
+    ep.row_stride = l.row_stride;
+    const Mat a{x, N, H, H}, b{w, V, H, H};
+    int rc;
+    if (use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+            rc = launch_tc<false, false, kBf16, EpiTopK>(d, cg, a, b, N, V, H, 1, ep, stream, 1, path.sched);
+        } else {
+            rc = LCE_ERR_ARG;
+        }
+    } else {
+        rc = launch_simt<T, EpiTopK>(d, a, false, b, false, N, V, H, ep, stream);
+    }
+    if (rc) return rc;
+    merge_topk_kernel<T><<<static_cast<int>(N), kTopkThreads, 0, stream>>>(
+        static_cast<const float*>(ws), static_cast<int>(l.n_tiles), use_tc ? kBN : kSimtBN, l.row_stride,
+        static_cast<int>(N), static_cast<const T*>(x), static_cast<const T*>(w), static_cast<int>(H),
+        static_cast<int>(V), scale, vocab_start, K, top_val, top_idx, lse);
+    LCE_COUNT_LAUNCH();
+    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
 // ---------------------------------------------------------------------------------------------
 // backward block plan
 // ---------------------------------------------------------------------------------------------
@@ -773,6 +814,41 @@ int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t 
             return greedy_head_impl<__half>(*d, path, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
         default:
             return greedy_head_impl<float>(*d, path, x, w, N, H, V, vocab_start, tok, logprob, lse, ws, s);
+    }
+}
+
+size_t lce_topk_workspace_bytes(int64_t N, int64_t H, int64_t V, int dtype, unsigned flags) {
+    if (check_dims(N, H, V, dtype)) return 0;
+    const bool tc_only = (flags & LCE_FLAG_FORCE_TC) != 0;  // else sized for the finer CUDA-core tiling
+    return align_up(topk_partial_bytes(N, V, tc_only), 256) + 256;
+}
+
+int lce_topk_head(const void* x, const void* w, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
+                  int k, float inv_temperature, float* top_val, int64_t* top_idx, float* lse, void* ws,
+                  size_t ws_bytes, unsigned flags, void* stream) {
+    int rc = check_dims(N, H, V, dtype);
+    if (rc) return rc;
+    if (k < 1 || k > kTopkMaxK || !(inv_temperature > 0.f)) return LCE_ERR_ARG;
+    if (N == 0) return LCE_OK;
+    if (!x || !w || !top_val || !top_idx || !lse || !ws) return LCE_ERR_ARG;
+    DeviceInfo* d;
+    if ((rc = device_info(&d))) return rc;
+    bool use_tc;
+    if ((rc = choose_path(dtype, H, x, w, flags, &use_tc))) return rc;
+    const size_t partial = topk_partial_bytes(N, V, use_tc);
+    if (ws_bytes < partial) return LCE_ERR_WS_TOO_SMALL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t sched_off = align_up(partial, 256);
+    const Path path{use_tc, cta_group_of(flags),
+                    ws_bytes >= sched_off + sizeof(int) ? reinterpret_cast<int*>(static_cast<char*>(ws) + sched_off) : nullptr};
+    long long* idx = reinterpret_cast<long long*>(top_idx);
+    switch (dtype) {
+        case LCE_DTYPE_BF16:
+            return topk_head_impl<__nv_bfloat16>(*d, path, x, w, N, H, V, vocab_start, k, inv_temperature, top_val, idx, lse, ws, s);
+        case LCE_DTYPE_F16:
+            return topk_head_impl<__half>(*d, path, x, w, N, H, V, vocab_start, k, inv_temperature, top_val, idx, lse, ws, s);
+        default:
+            return topk_head_impl<float>(*d, path, x, w, N, H, V, vocab_start, k, inv_temperature, top_val, idx, lse, ws, s);
     }
 }
 

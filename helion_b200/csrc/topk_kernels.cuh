@@ -1,0 +1,157 @@
+// Per-row merge of the sampling head: the records EpiTopK wrote per (vocab tile, row) -> the k largest
+// scaled logits of the row with their vocabulary indices (larger first; lower index first on ties) and the
+// row's logsumexp. One CTA per row.
+//
+// Every candidate is packed into one 64-bit key whose unsigned order is the wanted order: the float's bits
+// made order-preserving in the high word, 0xffffffff - column in the low word. Key 0 is "nothing".
+// The CTA keeps the best kTopkMaxK keys seen so far at the front of a shared-memory array and folds further
+// candidates in by sorting them together with that front (bitonic, descending).
+//
+// Exactness: a tile delivered only its kTileTop best. If the weakest of those still outranks the current
+// k-th key, the tile may hide entries that belong to the result; the CTA then recomputes that tile's logits
+// itself (dot products on the CUDA cores, fp32 accumulation), replaces the tile's entries and folds all of
+// them in. The k-th key only rises while entries are folded in, so one pass over the tiles settles it.
+#pragma once
+
+#include "epilogues.cuh"
+#include "row_kernels.cuh"
+
+namespace lce {
+
+constexpr int kTopkThreads = 256;
+constexpr int kTopkMaxK = 64;
+constexpr int kTopkSortN = 4096;  // keys sorted at a time: 32 KB of shared memory
+
+__device__ __forceinline__ unsigned long long topk_key(float v, int col) {
+    unsigned u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - static_cast<unsigned>(col));
+}
+__device__ __forceinline__ float topk_key_value(unsigned long long key) {
+    unsigned u = static_cast<unsigned>(key >> 32);
+    u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ int topk_key_col(unsigned long long key) {
+    return static_cast<int>(0xffffffffu - static_cast<unsigned>(key & 0xffffffffull));
+}
+
+// Bitonic sort of n keys (n a power of two) in shared memory, largest first, by the whole CTA.
+__device__ __forceinline__ void topk_sort_desc(unsigned long long* keys, int n) {
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n / 2; i += blockDim.x) {
+                const int lo = 2 * i - (i & (stride - 1));
+                const int hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const unsigned long long a = keys[lo], b = keys[hi];
+                if ((a < b) == desc) {
+                    keys[lo] = b;
+                    keys[hi] = a;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int topk_pow2_at_least(int n) {
+    int p = 64;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+// partial: [n_tiles][kTopRecord][row_stride] (EpiTopK), bn = tile width the GEMM core used.
+// top_val / top_idx: [N][K] (scaled logits, global vocabulary indices; -inf / -1 where the shard has fewer
+// than K columns). lse_out: [N] logsumexp of the scaled logits of this shard.
+template <class T>
+__global__ void __launch_bounds__(kTopkThreads)
+merge_topk_kernel(const float* __restrict__ partial, int n_tiles, int bn, long long row_stride, int N,
+                  const T* __restrict__ x, const T* __restrict__ w, int H, int V, float scale, long long vocab_start,
+                  int K, float* __restrict__ top_val, long long* __restrict__ top_idx, float* __restrict__ lse_out) {
+    __shared__ unsigned long long keys[kTopkSortN];
+    __shared__ float red_m[kTopkThreads / 32], red_s[kTopkThreads / 32];
+    const int row = blockIdx.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const float* rec = partial + row;
+
+    // ---- logsumexp of the row: thread t folds tiles t, t + 256, ..., then lanes and warps in a fixed order
+    {
+        float m = -INFINITY, s = 0.f;
+        for (int b = t; b < n_tiles; b += kTopkThreads) {
+            const float* base = rec + static_cast<long long>(b) * kTopRecord * row_stride;
+            merge_ms(m, s, base[0], base[row_stride]);
+        }
+        for (int off = 1; off < 32; off <<= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, off), os = __shfl_xor_sync(0xffffffffu, s, off);
+            merge_ms(m, s, om, os);
+        }
+        if (lane == 0) {
+            red_m[warp] = m;
+            red_s[warp] = s;
+        }
+        __syncthreads();
+        if (t == 0) {
+            for (int k = 1; k < kTopkThreads / 32; ++k) merge_ms(m, s, red_m[k], red_s[k]);
+            lse_out[row] = m + logf(s);
+        }
+    }
+
+    // ---- the k best of the tiles' candidates
+    for (int i = t; i < kTopkMaxK; i += kTopkThreads) keys[i] = 0ull;
+    const int total = n_tiles * kTileTop;
+    const int per_pass = kTopkSortN - kTopkMaxK;
+    for (int base = 0; base < total; base += per_pass) {
+        const int cnt = min(per_pass, total - base);
+        const int n = topk_pow2_at_least(kTopkMaxK + cnt);
+        __syncthreads();
+        for (int i = t; i < n - kTopkMaxK; i += kTopkThreads) {
+            unsigned long long key = 0ull;
+            if (i < cnt) {
+                const int tile = (base + i) / kTileTop, slot = (base + i) % kTileTop;
+                const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+                const int col = __float_as_int(r0[(2 + kTileTop + slot) * row_stride]);
+                if (col >= 0) key = topk_key(r0[(2 + slot) * row_stride], col);
+            }
+            keys[kTopkMaxK + i] = key;
+        }
+        topk_sort_desc(keys, n);
+    }
+
+    // ---- repair: tiles whose weakest kept entry still outranks the k-th key are recomputed in full
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+        const int last_col = __float_as_int(r0[(2 + 2 * kTileTop - 1) * row_stride]);
+        if (last_col < 0) continue;  // the tile has fewer than kTileTop columns: all of them were delivered
+        const unsigned long long last_key = topk_key(r0[(2 + kTileTop - 1) * row_stride], last_col);
+        if (last_key <= keys[K - 1]) continue;  // (uniform: every thread reads the same two values)
+        __syncthreads();
+        const int col0 = tile * bn;
+        for (int i = t; i < kTopkMaxK; i += kTopkThreads) {
+            const unsigned long long key = keys[i];
+            const int c = topk_key_col(key);
+            if (key != 0ull && c >= col0 && c < col0 + bn) keys[i] = 0ull;  // superseded by the recomputed values
+        }
+        const int n = topk_pow2_at_least(kTopkMaxK + bn);
+        for (int i = t; i < n - kTopkMaxK; i += kTopkThreads)
+            if (i >= bn || col0 + i >= V) keys[kTopkMaxK + i] = 0ull;
+        const T* xr = x + static_cast<long long>(row) * H;
+        for (int c = warp; c < bn && col0 + c < V; c += kTopkThreads / 32) {
+            const T* wr = w + static_cast<long long>(col0 + c) * H;
+            float acc = 0.f;
+            for (int k = lane; k < H; k += 32) acc = fmaf(Cvt<T>::to_f(xr[k]), Cvt<T>::to_f(wr[k]), acc);
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0) keys[kTopkMaxK + c] = topk_key(acc * scale, col0 + c);
+        }
+        topk_sort_desc(keys, n);
+    }
+
+    for (int i = t; i < K; i += kTopkThreads) {
+        const unsigned long long key = keys[i];
+        top_val[static_cast<long long>(row) * K + i] = key ? topk_key_value(key) : -INFINITY;
+        top_idx[static_cast<long long>(row) * K + i] = key ? vocab_start + topk_key_col(key) : -1ll;
+    }
+}
+
+}  // namespace lce

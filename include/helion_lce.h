@@ -244,6 +244,20 @@ int lce_greedy_head(const void* x, const void* w, int64_t N, int64_t H, int64_t 
                     int64_t* token, float* logprob, float* lse, void* ws, size_t ws_bytes, unsigned flags,
                     void* stream);
 
+/* Sampling head: for every row the k (1..64) largest SCALED logits y = inv_temperature * x . w[v] with their
+ * GLOBAL vocabulary indices (vocab_start + local row of w), largest first and the lower index first among
+ * equal values, and lse[i] = logsumexp_v y[i, v] over this shard - what temperature / top-k / nucleus
+ * sampling needs, without the N x V logits reaching memory. top_val is float32 [N, k], top_idx int64 [N, k]
+ * (-inf / -1 where the shard has fewer than k rows), lse float32 [N]. The result is exact: a vocabulary tile
+ * that holds more of the k best than the GEMM epilogue keeps per tile (8) is detected in the per-row merge and
+ * recomputed there. Takes the place of the reference's decode step, which forms all logits with
+ * tritium.matmul_vec on lm_head.T.contiguous() and runs torch.topk / torch.sort over them
+ * (examples/common.py:288-301, 380-396). ws: lce_topk_workspace_bytes(). */
+size_t lce_topk_workspace_bytes(int64_t N, int64_t H, int64_t V_local, int dtype, unsigned flags);
+int lce_topk_head(const void* x, const void* w, int64_t N, int64_t H, int64_t V_local, int64_t vocab_start,
+                  int dtype, int k, float inv_temperature, float* top_val, int64_t* top_idx, float* lse,
+                  void* ws, size_t ws_bytes, unsigned flags, void* stream);
+
 /* ---- producer of the hidden states -----------------------------------------------------------------
  * lce_rmsnorm_forward replaces the launches of tritium.rmsnorm and tritium.residual_rmsnorm
  * (tritium/ops/rmsnorm.py:29-84, :325-349, :749-778) on [n_rows, hidden] row-major tensors of `dtype`:

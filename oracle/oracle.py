@@ -391,3 +391,39 @@ def shard_backward_chunked(hidden: torch.Tensor, weight_shard: torch.Tensor, tar
         dx[r0:r1] = g @ w32
         dw += g.T @ h32[r0:r1]
     return {"dx": dx, "dw": dw, "stats": stats}
+
+
+def topk_expression(hidden: torch.Tensor, weight: torch.Tensor, k: int, temperature: float = 1.0) -> dict:
+    """Ground truth of the sampling head: the ``k`` largest of ``hidden @ weight.T / temperature`` in fp32 (largest
+    first, lower index first among equal values), their indices, and the logsumexp of the scaled logits - what the
+    reference's decode step obtains from materialised logits with ``torch.topk`` (examples/common.py:288-289)."""
+    y = (hidden.detach().float().reshape(-1, hidden.shape[-1]) @ weight.detach().float().T) / temperature
+    order = torch.sort(y, dim=1, descending=True, stable=True).indices[:, :k]
+    shape = tuple(hidden.shape[:-1])
+    return {"values": y.gather(1, order).reshape(shape + (order.shape[1],)),
+            "indices": order.reshape(shape + (order.shape[1],)),
+            "lse": torch.logsumexp(y, dim=1).reshape(shape), "logits": y}
+
+
+def reference_sampling_distribution(logits: torch.Tensor, *, temperature: float, top_k: int, top_p: float,
+                                    repetition_penalty: float, seen_token_ids) -> torch.Tensor:
+    """The probability vector the reference's ``sample_next_token`` draws from (examples/common.py:263-306),
+    restated for one row of unscaled fp32 logits: repetition penalty, temperature, top-k mask, nucleus mask,
+    softmax. Everything up to (not including) its ``torch.multinomial`` call."""
+    z = logits.float().reshape(-1).clone()
+    if repetition_penalty != 1.0 and seen_token_ids:
+        ids = torch.tensor(sorted(set(int(i) for i in seen_token_ids)), device=z.device)
+        sel = z[ids]
+        z[ids] = torch.where(sel < 0, sel * repetition_penalty, sel / repetition_penalty)
+    z = z / temperature
+    if 0 < top_k < z.numel():
+        threshold = torch.topk(z, top_k).values[-1]
+        z = z.masked_fill(z < threshold, -math.inf)
+    if top_p < 1.0:
+        sorted_z, sorted_i = torch.sort(z, descending=True)
+        cumulative = torch.softmax(sorted_z, dim=-1).cumsum(dim=-1)
+        remove = cumulative > top_p
+        remove[1:] = remove[:-1].clone()
+        remove[0] = False
+        z = z.scatter(0, sorted_i[remove], torch.full_like(sorted_z[remove], -math.inf))
+    return torch.softmax(z, dim=-1)

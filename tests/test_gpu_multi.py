@@ -106,6 +106,14 @@ def _worker(rank: int, world: int, port: int, results, dx_reduce: str) -> None:
                 torch.cuda.synchronize()
                 assert torch.equal(tok, tok_full)
                 torch.testing.assert_close(lp, lp_full, rtol=1e-5, atol=1e-5)
+                # ... and so are the k best candidates of the sampling head
+                val_full, idx_full, lse_full = decode_ops.topk_head(x.detach(), w_full.detach(), 16, temperature=0.9)
+                val, idx, lse = decode_ops.topk_head(xs.detach(), w_loc.detach(), 16, temperature=0.9,
+                                                     process_group=group, **kw)
+                torch.cuda.synchronize()
+                assert torch.equal(idx, idx_full)
+                torch.testing.assert_close(val, val_full, rtol=1e-6, atol=1e-6)
+                torch.testing.assert_close(lse, lse_full, rtol=1e-5, atol=1e-5)
                 assert _lib.device_status() == 0
             except Exception:  # noqa: BLE001
                 verdict = "error: " + traceback.format_exc(limit=4)
