@@ -38,7 +38,7 @@ SIGNATURES = {
     "lce_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t]),
     "lce_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                              c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
-                             c_uint, c_size_t, c_void_p, c_void_p, c_void_p]),
+                             c_uint, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]),
     "lce_dx_reduce_gather": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "lce_dx_reduce_slice": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "lce_backward_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_uint, c_size_t, c_void_p, c_void_p,

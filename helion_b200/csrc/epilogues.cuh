@@ -380,12 +380,20 @@ struct EpiStore {
         int peer_world, peer_rank;
         int rows_per_rank;
         int row_off;
+        // Optional sum of squares of the FINAL output values as stored (after rounding to T), for the gradient
+        // norm: every (tile, warp) writes one partial, sumsq_partial[((sumsq_tile0 + m_tile) * n_tiles + n_tile)
+        // * 4 + warp]; a later pass adds the partials in index order. Which CTA computes a tile does not matter,
+        // so the total is the same on every run. nullptr = off. Only in the modes that produce final values.
+        float* sumsq_partial = nullptr;
+        int sumsq_tile0 = 0;
     };
     struct State {
         int row;
         T* dst;  // start of this thread's output row
+        float sq;
     };
     static __device__ __forceinline__ void begin(State& st, const Params& p, const TileCtx& tc) {
+        st.sq = 0.f;
         st.row = tc.m_tile * kBM + tc.row_in_tile;
         if (p.peer_world > 0) {
             const int g = p.row_off + st.row;
@@ -450,8 +458,24 @@ struct EpiStore {
         }
         if (st.row >= p.rows || gcol0 >= p.cols) return;
         store_row32<T>(st.dst + gcol0, v, p.cols - gcol0);
+        if (p.sumsq_partial != nullptr) {
+            const int valid = p.cols - gcol0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float r = Cvt<T>::to_f(Cvt<T>::from_f(v[j]));  // the value as stored
+                if (j < valid) st.sq = fmaf(r, r, st.sq);
+            }
+        }
     }
-    static __device__ __forceinline__ void end(State&, const Params&, const TileCtx&) {}
+    static __device__ __forceinline__ void end(State& st, const Params& p, const TileCtx& tc) {
+        if (p.sumsq_partial == nullptr || (p.mode != kStoreDirect && p.mode != kStoreLast)) return;
+        float sq = st.sq;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        if ((tc.row_in_tile & 31) == 0 && tc.m_tile * kBM < p.rows)
+            p.sumsq_partial[(static_cast<long long>(p.sumsq_tile0 + tc.m_tile) * tc.n_tiles + tc.n_tile) * 4 +
+                            (tc.row_in_tile >> 5)] = sq;
+    }
 };
 
 }  // namespace lce

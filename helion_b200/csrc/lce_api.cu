@@ -495,7 +495,8 @@ struct BwdPlan {
     long long n_rblk, n_cblk;  // number of row chunks / vocab bands
     long long ldg;             // pitch of the G block in elements
     long long bn;              // tile width of the dX / dW GEMMs (for the scratch layout)
-    size_t off_count, off_rowscale, off_g, off_dx_scratch, off_dw_scratch, total;
+    size_t off_count, off_rowscale, off_g, off_dx_scratch, off_dw_scratch, off_sumsq, total;
+    long long sumsq_floats;      // partial sums of squares of dW: one per (128-row tile, tile column, warp)
     long long dw_band_scratch_floats;
     int dx_splits;               // k slices of the dX GEMM when one band covers the vocabulary
     long long dx_slab_floats;    // fp32 scratch of one dX row chunk (one slice)
@@ -560,6 +561,12 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
         off += align_up(static_cast<size_t>(p.n_cblk) * p.dw_band_scratch_floats * sizeof(float), 256);
     else if (need_dw && p.dw_splits > 1)  // slices of one band at a time
         off += align_up(static_cast<size_t>(p.dw_splits) * p.dw_band_scratch_floats * sizeof(float), 256);
+    p.off_sumsq = off;
+    p.sumsq_floats = cdiv(V, kBM) * cdiv(H, p.bn) * 4;
+    if (need_dw) {
+        const long long standalone = kSumsqBlocks;  // a split dW contraction takes the separate sum-of-squares pass
+        off += align_up(static_cast<size_t>(p.sumsq_floats > standalone ? p.sumsq_floats : standalone) * sizeof(float), 256);
+    }
     p.total = off;
     return p;
 }
@@ -574,7 +581,7 @@ template <class T, class TDx>
 int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const void* x, const void* w,
                   const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
                   long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, void* const* dx_events,
-                  const lce_peer_scatter* scatter, cudaStream_t stream) {
+                  const lce_peer_scatter* scatter, float* dw_sumsq, cudaStream_t stream) {
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
     const bool use_tc = path.use_tc;
     const int cg = path.cg;
@@ -676,6 +683,10 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 ep.mode = store_mode(rb, p.n_rblk);
                 ep.slab_floats = p.dw_band_scratch_floats;
                 ep.peer_world = 0;
+                if (dw_sumsq != nullptr && p.dw_splits == 1) {  // gradient-norm partials ride on the final stores
+                    ep.sumsq_partial = reinterpret_cast<float*>(ws + p.off_sumsq);
+                    ep.sumsq_tile0 = static_cast<int>(c0 / kBM);
+                }
                 const Mat b{xp + r0 * H, nr, H, H};
                 // short vocabulary block (few output tiles): cut the token contraction into slices
                 const int wsplits = (p.dw_splits > 1 && p.n_rblk == 1 && nc == p.nc) ? p.dw_splits : 1;
@@ -704,6 +715,19 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 }
             }
         }
+    }
+    if (dw_sumsq != nullptr && need_dw) {
+        float* partials = reinterpret_cast<float*>(ws + p.off_sumsq);
+        int count = static_cast<int>(p.sumsq_floats);
+        if (p.dw_splits > 1) {  // dW came out of the split-K reduction: one read of it, as lce_sumsq does
+            sumsq_partial_kernel<T><<<kSumsqBlocks, kOptThreads, 0, stream>>>(static_cast<const T*>(dw), V * H, partials);
+            LCE_COUNT_LAUNCH();
+            if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+            count = kSumsqBlocks;
+        }
+        sumsq_final_kernel<<<1, 1024, 0, stream>>>(partials, count, dw_sumsq, 0);
+        LCE_COUNT_LAUNCH();
+        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }
@@ -965,7 +989,7 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
                  const float* grad_out, int64_t N, int64_t H, int64_t V, int64_t vocab_start, int dtype,
                  int64_t ignore_index, int reduction, void* dx, void* dw, void* ws, size_t ws_bytes,
                  unsigned flags, size_t block_bytes, void* const* dx_events, const lce_peer_scatter* scatter,
-                 void* stream) {
+                 float* dw_sumsq, void* stream) {
     int rc = check_dims(N, H, V, dtype);
     if (rc) return rc;
     if (reduction != LCE_REDUCTION_NONE && reduction != LCE_REDUCTION_MEAN && reduction != LCE_REDUCTION_SUM)
@@ -979,6 +1003,7 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
             if (!scatter->staging[k] || !aligned16(scatter->staging[k])) return LCE_ERR_ARG;
     }
     if ((need_dx && !dx && !scatter && N > 0) || (need_dw && !dw)) return LCE_ERR_ARG;
+    if (dw_sumsq && need_dw && !aligned16(dw)) return LCE_ERR_ALIGN;
     DeviceInfo* d;
     if ((rc = device_info(&d))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -986,6 +1011,7 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
         // no rows: dW is all zeros (tritium/ops/cross_entropy.py:912-913), dX is empty
         if (need_dw && cudaMemsetAsync(dw, 0, static_cast<size_t>(V) * H * elem_size(dtype), s) != cudaSuccess)
             return LCE_ERR_CUDA;
+        if (need_dw && dw_sumsq && cudaMemsetAsync(dw_sumsq, 0, sizeof(float), s) != cudaSuccess) return LCE_ERR_CUDA;
         return LCE_OK;
     }
     if (!x || !w || !target || !lse || !grad_out || !ws) return LCE_ERR_ARG;
@@ -1015,9 +1041,9 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     const Path path{use_tc, cta_group_of(flags), reinterpret_cast<int*>(wsc + p.off_count + 128)};
 #define LCE_BWD(T)                                                                                          \
     (dx32 ? backward_impl<T, float>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
-                                    dx, dw, wsc, flags, dx_events, scatter, s)                              \
+                                    dx, dw, wsc, flags, dx_events, scatter, dw_sumsq, s)                    \
           : backward_impl<T, T>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
-                                dw, wsc, flags, dx_events, nullptr, s))
+                                dw, wsc, flags, dx_events, nullptr, dw_sumsq, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
         case LCE_DTYPE_F16: return LCE_BWD(__half);

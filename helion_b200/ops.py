@@ -22,7 +22,7 @@ from typing import Any
 
 import torch
 
-from . import _lib, parallel
+from . import _lib, grad_norm, parallel
 
 FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
 INDEX_DTYPES = (torch.int32, torch.int64)
@@ -337,15 +337,19 @@ def _backward(grad_out: torch.Tensor, hidden2d: torch.Tensor, weight: torch.Tens
     if need_dx and peers is None:  # with peer buffers nothing is written locally: rows leave through the epilogue
         dx = torch.empty((n_rows, hidden_size), dtype=torch.float32 if sharded else hidden2d.dtype, device=dev)
 
+    # the head's share of the gradient norm, summed up by the dW epilogue while it stores (no second read of dW)
+    dw_sumsq = torch.empty((), dtype=torch.float32, device=dev) if (dw is not None and grad_norm.enabled()) else None
     with _on_device(dev):
         _lib.check(
             L.lce_backward(hidden2d.data_ptr(), weight.data_ptr(), target1d.data_ptr(),
                            int(target1d.dtype == torch.int64), logsumexp.data_ptr(), grad_out.data_ptr(), n_rows,
                            hidden_size, v_local, vstart, dtype, ignore_index, red, _ptr(dx), _ptr(dw), ws.data_ptr(),
                            ws.numel(), flags, block, event_array, ctypes.byref(scatter) if scatter is not None else None,
-                           _stream(dev)),
+                           _ptr(dw_sumsq), _stream(dev)),
             "lce_backward",
         )
+    if dw_sumsq is not None:
+        grad_norm.remember(dw, dw_sumsq)
     if peers is not None:
         dx = _finish_peer_reduce(peers, staging_index, events, n_rows, hidden_size, hidden2d.dtype, dev)
     elif sharded and dx is not None:

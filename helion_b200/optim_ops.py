@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, grad_norm
 from .ops import FLOAT_DTYPES, _DTYPE_CODE, _need_cuda, _need_dtype, _on_device, _stream, _workspace
 
 
@@ -63,17 +63,30 @@ def adamw_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, e
 
 
 def grad_sumsq(tensors: list[torch.Tensor]) -> torch.Tensor:
-    """Sum of squares of all elements of ``tensors`` as a 0-dim float32 device tensor (fixed summation order)."""
+    """Sum of squares of all elements of ``tensors`` as a 0-dim float32 device tensor (fixed summation order).
+    A gradient whose producing kernel already summed its squares (``grad_norm``: the LM-head gradient of the
+    fused loss, when enabled) is not read again; its remembered sum is added instead."""
     dev = tensors[0].device
     L = _lib.lib()
     out = torch.empty((), dtype=torch.float32, device=dev)
     ws = _workspace(L.lce_sumsq_workspace_bytes(), dev)
+    known = []
+    started = False
     with _on_device(dev):
-        for i, t in enumerate(tensors):
+        for t in tensors:
             if t.dtype not in _DTYPE_CODE or not t.is_contiguous():
                 raise ValueError("grad_sumsq needs contiguous float16 / bfloat16 / float32 CUDA tensors.")
-            _lib.check(L.lce_sumsq(t.data_ptr(), t.numel(), _DTYPE_CODE[t.dtype], out.data_ptr(), int(i > 0),
+            have = grad_norm.lookup(t)
+            if have is not None:
+                known.append(have)
+                continue
+            _lib.check(L.lce_sumsq(t.data_ptr(), t.numel(), _DTYPE_CODE[t.dtype], out.data_ptr(), int(started),
                                    ws.data_ptr(), ws.numel(), _stream(dev)), "lce_sumsq")
+            started = True
+    if not started:
+        out.zero_()
+    for have in known:  # device scalars, added in list order
+        out = out + have
     return out
 
 

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LCE_VERSION 1
+#define LCE_VERSION 2
 
 /* element type of x, w, dx, dw */
 #define LCE_DTYPE_BF16 0
@@ -147,7 +147,12 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
  * partial sums over blocks are added in a fixed order in fp32, so results are deterministic.
  * dx_events: NULL, or one cudaEvent_t per row chunk of lce_backward_plan(); event i is recorded on
  * `stream` as soon as the dx rows of chunk i are final (before the remaining dW work), so that a
- * caller can start reducing partial dx across ranks on another stream while this call's GEMMs run. */
+ * caller can start reducing partial dx across ranks on another stream while this call's GEMMs run.
+ * dw_sumsq: NULL, or one float that receives the sum of squares of dw as stored (the head's share of the
+ * gradient norm that helion.clip_grad_norm computes, helion/training.py:36-49, by reading every gradient
+ * again): the dW GEMM's epilogue adds up the squares of the values it stores, one partial per (tile, warp),
+ * and a last small launch adds the partials in index order - no second pass over the V x H gradient, and the
+ * same bits on every run. dw must then be 16-byte aligned. */
 /* Optional fusion of the cross-rank dX reduction into the dX GEMM (vocabulary-parallel runs; new, the
  * reference is single-GPU). With a non-NULL `scatter` (and LCE_FLAG_DX_F32) lce_backward does not write
  * `dx`: the epilogue of the dX GEMM stores every finished fp32 row directly into the staging buffer of
@@ -183,7 +188,7 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
                  const float* lse, const float* grad_out, int64_t N, int64_t H, int64_t V_local,
                  int64_t vocab_start, int dtype, int64_t ignore_index, int reduction, void* dx,
                  void* dw, void* ws, size_t ws_bytes, unsigned flags, size_t block_bytes,
-                 void* const* dx_events, const lce_peer_scatter* scatter, void* stream);
+                 void* const* dx_events, const lce_peer_scatter* scatter, float* dw_sumsq, void* stream);
 
 /* The block grid lce_backward will use for these arguments (x and w only decide, by their
  * alignment, which kernel family runs): out[0] = rows per row chunk, out[1] = vocabulary columns per

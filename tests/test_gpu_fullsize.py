@@ -130,7 +130,7 @@ def test_14b_class_shard_of_one_rank_full_size():
         ws = Guarded(L.lce_backward_workspace_bytes(n, h, v_loc, code, 0, 0))
         _lib.check(L.lce_backward(x.data_ptr(), w_loc.data_ptr(), t.data_ptr(), 1, full["lse"].data_ptr(), go.data_ptr(),
                                   n, h, v_loc, start, code, -100, _lib.REDUCTION_SUM, dx.ptr, dw.ptr, ws.ptr, ws.nbytes,
-                                  0, 0, None, None, stream()), "lce_backward")
+                                  0, 0, None, None, None, stream()), "lce_backward")
         torch.cuda.synchronize()
         assert dx.intact() and dw.intact() and ws.intact()
         runs.append((dx.view(torch.bfloat16, (n, h)).clone(), dw.view(torch.bfloat16, (v_loc, h)).clone()))

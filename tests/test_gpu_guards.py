@@ -61,7 +61,7 @@ def test_fused_loss_forward_and_backward_stay_inside_their_buffers(dtype, flags,
     bws = Guarded(L.lce_backward_workspace_bytes(n, h, v, code, flags, 0))
     _lib.check(L.lce_backward(x.data_ptr(), w.data_ptr(), t.data_ptr(), 1, lse.ptr, go.data_ptr(), n, h, v, 0, code,
                               -100, _lib.REDUCTION_MEAN, dx.ptr, dw.ptr, bws.ptr, bws.nbytes, flags, 0, None, None,
-                              stream()), "lce_backward")
+                              None, stream()), "lce_backward")
     tok, lp = Guarded(n * 8), Guarded(n * 4)
     gws = Guarded(L.lce_forward_workspace_bytes(n, h, v, code, flags))
     _lib.check(L.lce_greedy_head(x.data_ptr(), w.data_ptr(), n, h, v, 0, code, tok.ptr, lp.ptr, None, gws.ptr,

@@ -88,3 +88,55 @@ def test_gradient_norm_is_deterministic_and_clipping_fuses_into_the_step(dtype):
     helion_b200.adamw_step(b, (prm.grad.float() * coef).to(dtype), m2, v2, lr=1e-2)
     tol = 1e-6 if dtype == torch.float32 else 8e-3
     torch.testing.assert_close(a.float(), b.float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("force", ["tc", "tc1", "simt"])
+@pytest.mark.parametrize("shape,block", [((300, 128, 1500), 0),        # one block, dW stored directly
+                                         ((1200, 256, 2100), 1_300_000),  # vocabulary bands
+                                         ((2100, 256, 1200), 1_100_000),  # row chunks: dW summed over chunks in fp32
+                                         ((4096, 256, 65), 0)])           # short vocabulary: dW contraction split
+def test_gradient_norm_from_the_dw_epilogue(shape, block, force, monkeypatch):
+    """The sum of squares the dW GEMM adds up while storing equals a separate pass over the stored gradient
+    (``lce_sumsq``; fp32 sums in two different fixed orders) and the float64 sum, is bit-identical from run to
+    run, and is what ``clip_grad_norm`` uses for the head - as helion.clip_grad_norm (helion/training.py:36-49
+    of the reference) would compute from the gradient."""
+    from helion_b200 import _lib, grad_norm, ops, optim_ops
+
+    monkeypatch.setenv("HELION_B200_FORCE", force)
+    monkeypatch.setenv("HELION_B200_BLOCK_BYTES", str(block))
+    n, h, v = shape
+    g = torch.Generator().manual_seed(n + v)
+    x = torch.randn(n, h, generator=g).bfloat16().to(DEV).requires_grad_(True)
+    w = (torch.randn(v, h, generator=g) * 0.1).bfloat16().to(DEV).requires_grad_(True)
+    t = torch.randint(0, v, (n,), generator=g).to(DEV)
+    grad_norm.enable(True)
+    try:
+        sums = []
+        for _ in range(2):
+            x.grad = w.grad = None
+            ops.linear_cross_entropy(x, w, t).backward(torch.tensor(37.0, device=DEV))
+            fused = grad_norm.lookup(w.grad)
+            assert fused is not None, "autograd handed the gradient over without a copy; its sum must be found"
+            sums.append(fused.clone())
+        assert torch.equal(sums[0], sums[1])
+        launches = _lib.lib().lce_launch_count()
+        via_registry = optim_ops.grad_sumsq([w.grad])
+        assert _lib.lib().lce_launch_count() == launches, "the head's gradient must not be read again"
+        assert torch.equal(via_registry, sums[0])
+        exact = float(w.grad.double().pow(2).sum())
+        assert abs(float(sums[0]) - exact) <= 1e-5 * exact
+        grad_norm.enable(False)
+        separate = optim_ops.grad_sumsq([w.grad])
+        assert _lib.lib().lce_launch_count() > launches
+        assert abs(float(separate) - float(sums[0])) <= 2e-6 * exact
+        # a gradient that was written after the backward no longer matches its remembered sum
+        grad_norm.enable(True)
+        x.grad = w.grad = None
+        ops.linear_cross_entropy(x, w, t).backward()
+        w.grad.mul_(2.0)
+        assert grad_norm.lookup(w.grad) is None
+        norm, coef = helion_b200.clip_grad_norm([x, w], 1.0)
+        ref = torch.sqrt(x.grad.double().pow(2).sum() + w.grad.double().pow(2).sum())
+        assert abs(float(norm) - float(ref)) <= 1e-5 * float(ref)
+    finally:
+        grad_norm.enable(False)

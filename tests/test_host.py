@@ -219,7 +219,7 @@ def test_null_pointers_and_bad_enums_are_argument_errors():
     L = _lib.lib()
     assert L.lce_forward_stats(None, None, None, 1, 8, 8, 8, 0, 0, None, None, 0, 0, None) == 1
     assert L.lce_forward_stats(None, None, None, 1, 8, 8, 8, 0, 7, None, None, 0, 0, None) == 1
-    assert L.lce_backward(None, None, None, 1, None, None, 8, 8, 8, 0, 0, -100, 9, None, None, None, 0, 0, 0, None, None, None) == 1
+    assert L.lce_backward(None, None, None, 1, None, None, 8, 8, 8, 0, 0, -100, 9, None, None, None, 0, 0, 0, None, None, None, None) == 1
     plan = (ctypes.c_int64 * 4)()
     assert L.lce_backward_plan(8192, 4096, 128256, 0, 0, 0, None, None, plan) == 0
     assert list(plan) == [8192, 16384, 1, 8]  # Llama-3 head: all rows, 8 vocabulary bands of 16384 columns
