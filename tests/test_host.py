@@ -186,7 +186,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(handle, name), name
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert handle.lce_version() == 1
+    assert handle.lce_version() == 2
     assert handle.lce_strerror(0) == b"ok"
     assert b"workspace" in handle.lce_strerror(3)
     assert isinstance(handle.lce_launch_count(), int)
