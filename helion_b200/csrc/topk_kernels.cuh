@@ -21,6 +21,7 @@ namespace lce {
 constexpr int kTopkThreads = 256;
 constexpr int kTopkMaxK = 64;
 constexpr int kTopkSortN = 4096;  // keys sorted at a time: 32 KB of shared memory
+constexpr int kTopkFlagBatch = 2048;  // tiles tested for repair at a time
 
 __device__ __forceinline__ unsigned long long topk_key(float v, int col) {
     unsigned u = __float_as_uint(v);
@@ -119,32 +120,47 @@ merge_topk_kernel(const float* __restrict__ partial, int n_tiles, int bn, long l
         topk_sort_desc(keys, n);
     }
 
-    // ---- repair: tiles whose weakest kept entry still outranks the k-th key are recomputed in full
-    for (int tile = 0; tile < n_tiles; ++tile) {
-        const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
-        const int last_col = __float_as_int(r0[(2 + 2 * kTileTop - 1) * row_stride]);
-        if (last_col < 0) continue;  // the tile has fewer than kTileTop columns: all of them were delivered
-        const unsigned long long last_key = topk_key(r0[(2 + kTileTop - 1) * row_stride], last_col);
-        if (last_key <= keys[K - 1]) continue;  // (uniform: every thread reads the same two values)
+    // ---- repair: tiles whose weakest kept entry still outranks the k-th key are recomputed in full.
+    // All tiles are tested at once against the k-th key as it stands (it only rises later, so this can flag a
+    // tile too many, never one too few); the flagged ones, usually none, are then taken one by one.
+    __shared__ int flagged[kTopkFlagBatch];
+    __shared__ int n_flagged;
+    for (int tile0 = 0; tile0 < n_tiles; tile0 += kTopkFlagBatch) {
+        if (t == 0) n_flagged = 0;
         __syncthreads();
-        const int col0 = tile * bn;
-        for (int i = t; i < kTopkMaxK; i += kTopkThreads) {
-            const unsigned long long key = keys[i];
-            const int c = topk_key_col(key);
-            if (key != 0ull && c >= col0 && c < col0 + bn) keys[i] = 0ull;  // superseded by the recomputed values
+        const unsigned long long kth = keys[K - 1];
+        for (int tile = tile0 + t; tile < min(n_tiles, tile0 + kTopkFlagBatch); tile += kTopkThreads) {
+            const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+            const int last_col = __float_as_int(r0[(2 + 2 * kTileTop - 1) * row_stride]);
+            // a tile with fewer than kTileTop columns delivered all of them
+            if (last_col >= 0 && topk_key(r0[(2 + kTileTop - 1) * row_stride], last_col) > kth)
+                flagged[atomicAdd(&n_flagged, 1)] = tile;
         }
-        const int n = topk_pow2_at_least(kTopkMaxK + bn);
-        for (int i = t; i < n - kTopkMaxK; i += kTopkThreads)
-            if (i >= bn || col0 + i >= V) keys[kTopkMaxK + i] = 0ull;
-        const T* xr = x + static_cast<long long>(row) * H;
-        for (int c = warp; c < bn && col0 + c < V; c += kTopkThreads / 32) {
-            const T* wr = w + static_cast<long long>(col0 + c) * H;
-            float acc = 0.f;
-            for (int k = lane; k < H; k += 32) acc = fmaf(Cvt<T>::to_f(xr[k]), Cvt<T>::to_f(wr[k]), acc);
-            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (lane == 0) keys[kTopkMaxK + c] = topk_key(acc * scale, col0 + c);
+        __syncthreads();
+        const int count = n_flagged;
+        for (int f = 0; f < count; ++f) {
+            const int tile = flagged[f];  // any order: the result is the k best of the same set of entries
+            const int col0 = tile * bn;
+            __syncthreads();
+            for (int i = t; i < kTopkMaxK; i += kTopkThreads) {
+                const unsigned long long key = keys[i];
+                const int c = topk_key_col(key);
+                if (key != 0ull && c >= col0 && c < col0 + bn) keys[i] = 0ull;  // superseded by the recomputed values
+            }
+            const int n = topk_pow2_at_least(kTopkMaxK + bn);
+            for (int i = t; i < n - kTopkMaxK; i += kTopkThreads)
+                if (i >= bn || col0 + i >= V) keys[kTopkMaxK + i] = 0ull;
+            const T* xr = x + static_cast<long long>(row) * H;
+            for (int c = warp; c < bn && col0 + c < V; c += kTopkThreads / 32) {
+                const T* wr = w + static_cast<long long>(col0 + c) * H;
+                float acc = 0.f;
+                for (int k = lane; k < H; k += 32) acc = fmaf(Cvt<T>::to_f(xr[k]), Cvt<T>::to_f(wr[k]), acc);
+                for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (lane == 0) keys[kTopkMaxK + c] = topk_key(acc * scale, col0 + c);
+            }
+            topk_sort_desc(keys, n);
         }
-        topk_sort_desc(keys, n);
+        __syncthreads();
     }
 
     for (int i = t; i < K; i += kTopkThreads) {

@@ -303,3 +303,42 @@ def test_oracle_greedy_expression_is_argmax_of_log_softmax():
     ls = torch.log_softmax(h.float().reshape(-1, 16) @ w.float().T, dim=-1)
     assert torch.equal(e["token"].reshape(-1), ls.argmax(dim=-1))
     torch.testing.assert_close(e["logprob"].reshape(-1), ls.max(dim=-1).values, rtol=1e-6, atol=1e-6)
+
+
+def test_grad_norm_hand_over_matches_only_the_untouched_gradient():
+    """The registry that hands the dW epilogue's sum of squares to grad_sumsq: a hit needs the same storage,
+    address, shape and version; a clone, a written tensor or a freed one miss; autograd's hand-over of a leaf
+    gradient (no copy) hits."""
+    from helion_b200 import grad_norm
+
+    grad_norm.enable(True)
+    try:
+        g, s = torch.randn(5, 3), torch.tensor(1.0)
+        grad_norm.remember(g, s)
+        assert grad_norm.lookup(g) is s
+        assert grad_norm.lookup(g.clone()) is None and grad_norm.lookup(g[:2]) is None
+        g.mul_(2.0)
+        assert grad_norm.lookup(g) is None
+
+        class Op(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x):
+                return x.sum()
+
+            @staticmethod
+            def backward(ctx, go):
+                dw = torch.full((4,), 2.0) * go
+                grad_norm.remember(dw, torch.tensor(16.0))
+                return dw
+
+        x = torch.zeros(4, requires_grad=True)
+        Op.apply(x).backward()
+        assert float(grad_norm.lookup(x.grad)) == 16.0
+        Op.apply(x).backward()  # accumulates into the existing .grad: the remembered sum no longer applies
+        assert grad_norm.lookup(x.grad) is None
+        for _ in range(3 * grad_norm.KEEP):
+            grad_norm.remember(torch.randn(2), s)
+        assert len(grad_norm._known) <= grad_norm.KEEP
+    finally:
+        grad_norm.enable(False)
+    assert not grad_norm._known
