@@ -50,6 +50,22 @@ def bench_ms(fn, repeats: int | None = None) -> float:
     return statistics.median(do_bench(fn) for _ in range(repeats))
 
 
+def loop_ms(fn, calls: int = 300) -> float:
+    """Wall time per call of ``calls`` back-to-back calls (one synchronise at the end), in ms: what a training
+    loop pays per call, host time included. For launch-bound shapes this, not the device time between two
+    events, is the throughput-relevant figure."""
+    import time
+
+    for _ in range(20):
+        fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        fn()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / calls * 1e3
+
+
 def tflops(flops: float, ms: float) -> float:
     return flops / (ms * 1e-3) / 1e12
 

@@ -28,7 +28,7 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 
 import helion_b200  # noqa: E402
-from benchmarks._utils import bench_ms, require_cuda, tflops  # noqa: E402
+from benchmarks._utils import bench_ms, loop_ms, require_cuda, tflops  # noqa: E402
 from helion_b200 import inputs  # noqa: E402
 
 # (n_rows, hidden_size, vocab_size), as in the reference harness (its lines 23-31)
@@ -84,6 +84,9 @@ def time_case(label: str, hidden, weight, target, providers, peak: float, eager_
                 stats = helion_b200.ops.local_stats(hidden.view(n, h), weight, target.view(n), 0)
                 _, lse, _ = helion_b200.ops.finalize(stats.view(1, 3, n), target.view(n), "mean", -100)
                 bwd = bench_ms(lambda: helion_b200.linear_cross_entropy_backward(grad_out, hidden, weight, target, lse))
+                if nhv < 1e11:  # launch-bound shapes: also the per-call time of back-to-back calls
+                    rec["fwd_loop_ms"] = loop_ms(lambda: helion_b200.linear_cross_entropy(hidden, weight, target))
+                    rec["bwd_loop_ms"] = loop_ms(lambda: helion_b200.linear_cross_entropy_backward(grad_out, hidden, weight, target, lse))
                 hg, wg = hidden.clone().requires_grad_(True), weight.clone().requires_grad_(True)
 
                 def both():
@@ -107,6 +110,10 @@ def time_case(label: str, hidden, weight, target, providers, peak: float, eager_
                     continue
                 bwd = bench_ms(lambda: tritium.linear_cross_entropy_backward(grad_out, hidden.view(n, h), weight,
                                                                              target.view(n), lse))
+                if nhv < 1e11:
+                    rec["fwd_loop_ms"] = loop_ms(lambda: tritium.linear_cross_entropy(hidden, weight, target))
+                    rec["bwd_loop_ms"] = loop_ms(lambda: tritium.linear_cross_entropy_backward(
+                        grad_out, hidden.view(n, h), weight, target.view(n), lse))
             else:
                 raise ValueError(f"Unknown provider: {provider}")
         except Exception as exc:  # noqa: BLE001 - one provider failing must not hide the others

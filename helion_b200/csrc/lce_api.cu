@@ -366,6 +366,11 @@ struct FwdOutputs {
     float* lse = nullptr;        // [N]       (fused finalize)
     float* loss_rows = nullptr;  // [N]       (fused finalize)
     long long ignore_index = -100;
+    // small batches: merge + finalize + loss reduction in one launch (then loss_rows is not used)
+    bool one_launch_tail = false;
+    int reduction = LCE_REDUCTION_MEAN;
+    float* loss = nullptr;         // () or [N]
+    float* valid_count = nullptr;  // optional
 };
 
 template <class T>
@@ -397,7 +402,11 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
     }
     if (rc) return rc;
     const int blocks = static_cast<int>(cdiv(N, kMergeRows)), threads = kMergeRows * kMergeLanes;
-    if (out.stats != nullptr)
+    if (out.one_launch_tail)
+        merge_finalize_small_kernel<<<1, 1024, 0, stream>>>(
+            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), tgt, tgt_i64,
+            out.ignore_index, out.reduction, out.lse, out.loss, out.valid_count);
+    else if (out.stats != nullptr)
         merge_partials_kernel<false><<<blocks, threads, 0, stream>>>(
             static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
             out.stats, nullptr, 0, 0, nullptr, nullptr);
@@ -937,6 +946,11 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
     fo.lse = lse;
     fo.loss_rows = reduction == LCE_REDUCTION_NONE ? loss : reinterpret_cast<float*>(static_cast<char*>(ws) + partial_bytes);
     fo.ignore_index = ignore_index;
+    // up to 1024 rows and a few hundred vocabulary tiles: one CTA finishes the whole forward after the GEMM
+    fo.one_launch_tail = N <= 1024 && fwd_layout(N, V, use_tc).n_tiles <= 512;
+    fo.reduction = reduction;
+    fo.loss = loss;
+    fo.valid_count = valid_count;
     const size_t sched_off = partial_bytes + align_up(static_cast<size_t>(N) * sizeof(float), 256);
     const Path path{use_tc, cta_group_of(flags),
                     ws_bytes >= sched_off + sizeof(int) ? reinterpret_cast<int*>(static_cast<char*>(ws) + sched_off) : nullptr};
@@ -951,7 +965,7 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
             rc = forward_stats_impl<float>(*d, path, x, w, target, target_is_i64, N, H, V, 0, fo, ws, s);
     }
     if (rc) return rc;
-    if (reduction != LCE_REDUCTION_NONE || valid_count) {
+    if (!fo.one_launch_tail && (reduction != LCE_REDUCTION_NONE || valid_count)) {
         reduce_loss_kernel<<<1, 1024, 0, s>>>(fo.loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
                                               reduction == LCE_REDUCTION_MEAN ? 1 : 0,
                                               reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);

@@ -62,6 +62,56 @@ merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long 
     }
 }
 
+// Small batches (N <= 1024) of an unsharded vocabulary: merge, finalize and the loss reduction in ONE launch
+// of one CTA. The 1024 threads form R = roundup(N, 32) row lanes x J = 1024 / R tile lanes (at most 32): tile
+// lane j folds tiles j, j + J, ... of its row in ascending order, tile lane 0 then folds the J results in lane
+// order, and the rows are added by the fixed tree of block_sum_1024 - the same bits on every run (not the
+// bits of the three-kernel path, which folds a row's tiles in a different, equally fixed order).
+__device__ __forceinline__ float block_sum_1024(float v, float* sh);
+
+__global__ void __launch_bounds__(1024)
+merge_finalize_small_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N,
+                            const void* tgt, int tgt_i64, long long ignore_index, int reduction,
+                            float* __restrict__ lse, float* __restrict__ loss, float* __restrict__ valid_count) {
+    __shared__ float sh[1024], sm[1024], ss[1024], st[1024];
+    const int R = (N + 31) / 32 * 32;
+    const int J = min(32, 1024 / R);
+    const int r = threadIdx.x % R, j = threadIdx.x / R;
+    float m = -INFINITY, s = 0.f, t = -INFINITY;
+    if (j < J && r < N) {
+        for (int b = j; b < n_tiles; b += J) {
+            const float* base = partial + static_cast<long long>(b) * 3 * row_stride + r;
+            merge_ms(m, s, base[0], base[row_stride]);
+            t = fmaxf(t, base[2 * row_stride]);
+        }
+    }
+    sm[threadIdx.x] = m;
+    ss[threadIdx.x] = s;
+    st[threadIdx.x] = t;
+    __syncthreads();
+    float nll = 0.f, cnt = 0.f;
+    if (j == 0 && r < N) {
+        for (int k = 1; k < J; ++k) {
+            merge_ms(m, s, sm[k * R + r], ss[k * R + r]);
+            t = fmaxf(t, st[k * R + r]);
+        }
+        const float l = m + logf(s);
+        lse[r] = l;
+        const bool valid = load_target(tgt, tgt_i64, r) != ignore_index;
+        nll = valid ? (l - t) : 0.f;
+        cnt = valid ? 1.f : 0.f;
+        if (reduction == 0) loss[r] = nll;  // LCE_REDUCTION_NONE
+    }
+    if (reduction == 0 && valid_count == nullptr) return;
+    const float total = block_sum_1024(nll, sh);
+    const float count = block_sum_1024(cnt, sh);
+    if (threadIdx.x == 0) {
+        if (reduction == 1) *loss = total / count;  // mean; count == 0 -> NaN, as torch
+        else if (reduction == 2) *loss = total;
+        if (valid_count) *valid_count = count;
+    }
+}
+
 // Greedy head: partial [n_tiles][3][row_stride] of EpiTop1 -> token[N] (global vocabulary index of the
 // largest logit; the lowest index on ties), logprob[N] = log softmax at that token, optionally lse[N].
 // Same CTA shape and fold order as merge_partials_kernel.

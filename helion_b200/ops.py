@@ -168,8 +168,26 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+_WS_CACHE_MAX = 32 << 20
+_ws_cache: dict[tuple[int, int], torch.Tensor] = {}
+
+
 def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    """Scratch for one C-ABI call. Small requests (latency-bound problems, where an allocation is a visible
+    share of the call) reuse one buffer per (device, stream): calls on one stream run in order, so they may
+    share scratch; calls on different streams get different buffers. Large requests are allocated per call and
+    go back to torch's caching allocator afterwards."""
+    nbytes = max(int(nbytes), 256)
+    if nbytes > _WS_CACHE_MAX:
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if len(_ws_cache) >= 64:  # streams come and go: do not let the cache grow without bound
+            _ws_cache.clear()
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
 
 
 def _resolve_vocab_start(vocab_start: int | None, process_group: Any, v_local: int, device: torch.device) -> int:
