@@ -946,8 +946,13 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
     fo.lse = lse;
     fo.loss_rows = reduction == LCE_REDUCTION_NONE ? loss : reinterpret_cast<float*>(static_cast<char*>(ws) + partial_bytes);
     fo.ignore_index = ignore_index;
-    // up to 1024 rows and a few hundred vocabulary tiles: one CTA finishes the whole forward after the GEMM
-    fo.one_launch_tail = N <= 1024 && fwd_layout(N, V, use_tc).n_tiles <= 512;
+    // few rows and few vocabulary tiles: one CTA finishes the whole forward after the GEMM, as long as each of
+    // its threads folds at most 16 tiles (1024 threads = roundup(N, 32) row lanes x tile lanes)
+    {
+        const long long row_lanes = cdiv(N, 32) * 32;
+        const long long tile_lanes = row_lanes <= 1024 ? (1024 / row_lanes < 32 ? 1024 / row_lanes : 32) : 0;
+        fo.one_launch_tail = tile_lanes > 0 && cdiv(fwd_layout(N, V, use_tc).n_tiles, tile_lanes) <= 16;
+    }
     fo.reduction = reduction;
     fo.loss = loss;
     fo.valid_count = valid_count;
