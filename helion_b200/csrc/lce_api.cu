@@ -1595,9 +1595,13 @@ RmsShape rms_shape(long long H, int dtype, bool all_aligned, int n_streams = 1) 
 
 // CTAs for a row kernel of `threads` threads: enough to keep every SM's thread slots full.
 int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) {
+    // HELION_B200_RMS_GRID_MULT (tuning knob): grid = this many times the resident CTAs; 0 = one CTA per row
+    // group, i.e. no persistence at all (the hardware deals the CTAs to the SMs as they retire)
+    static const int kGridMult = [] { const char* e = getenv("HELION_B200_RMS_GRID_MULT"); return e ? atoi(e) : 1; }();
     long long per_sm = 2048 / threads;
     if (per_sm > 16) per_sm = 16;
     long long g = static_cast<long long>(d.sm_count) * per_sm;
+    g = kGridMult > 0 ? g * kGridMult : n_rows;
     if (cap > 0 && g > cap) g = cap;
     return static_cast<int>(n_rows < g ? n_rows : g);
 }
@@ -1694,6 +1698,13 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     {
         RmsRingPlan rp;
         if (rms_forward_uses_ring(sh, n_rows, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, RESIDUAL, &rp)) {
+            static std::atomic<bool> hint_set[kMaxDevices];
+            if (!hint_set[d.index].load(std::memory_order_acquire)) {
+                const char* e = getenv("HELION_B200_RMS_HINT");
+                const int hint = e ? atoi(e) : 0;
+                if (hint != 0 && cudaMemcpyToSymbol(g_rms_hint, &hint, sizeof(int)) != cudaSuccess) return LCE_ERR_CUDA;
+                hint_set[d.index].store(true, std::memory_order_release);
+            }
             const int grid = rms_ring_grid(d, sh, rp, n_rows, 0);
             int rc = LCE_OK;
 #define LCE_RMS_RING_FWD(VPT)                                                                             \

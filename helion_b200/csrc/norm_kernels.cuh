@@ -271,6 +271,10 @@ constexpr int kRmsMaxStages = 4;
 constexpr int kRmsRingBytesPerSm = 200 * 1024;
 constexpr int kDevErrNormTimeout = 111;
 
+// Streaming hints of the ring forward (experiment knob, set from HELION_B200_RMS_HINT at first use):
+// bit 0 = the bulk loads carry an L2 evict_first policy, bit 1 = the outputs are stored with st.global.cs.
+__device__ int g_rms_hint = 0;
+
 struct RmsRing {
     uint64_t full[kRmsMaxStages];
     int abort_flag;
@@ -292,6 +296,13 @@ __device__ __forceinline__ void rms_ring_issue(RmsRing& ring, unsigned char* dat
     // g_debug_announce_extra is 0 except in the wait-expiry test (a read of a cached word per row group)
     ptx::mbar_arrive_expect_tx(bar, nr * row_bytes * NS + ptx::g_debug_announce_extra);
     unsigned char* dst = data + static_cast<size_t>(s) * (ROWS * NS * row_bytes);
+    if (g_rms_hint & 1) {
+        const uint64_t policy = ptx::make_l2_policy(ptx::kL2EvictFirst);
+#pragma unroll
+        for (int n = 0; n < NS; ++n)
+            ptx::bulk_load_1d_hint(ptx::smem_u32(dst + n * ROWS * row_bytes), src[n] + row0 * H, nr * row_bytes, bar, policy);
+        return;
+    }
 #pragma unroll
     for (int n = 0; n < NS; ++n)
         ptx::bulk_load_1d(ptx::smem_u32(dst + n * ROWS * row_bytes), src[n] + row0 * H, nr * row_bytes, bar);
@@ -326,6 +337,7 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ weight, T
     const long long n_groups = (static_cast<long long>(n_rows) + ROWS - 1) / ROWS;
     const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
     const T* const srcs[1] = {x};
+    const bool stream_stores = (g_rms_hint & 2) != 0;
 
     if (t == 0) {
         for (int s = 0; s < stages; ++s) ptx::mbar_init(ptx::smem_u32(&ring.full[s]), 1);
@@ -387,7 +399,8 @@ rms_ring_forward_kernel(const T* __restrict__ x, const T* __restrict__ weight, T
                         if (!kWeightUnpacked) rms_unpack<T>(wraw[i], w);
 #pragma unroll
                         for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * (kWeightUnpacked ? wf[i][j] : w[j]);
-                        *reinterpret_cast<uint4*>(out + (row0 + r) * H + c) = rms_pack<T>(z);
+                        if (stream_stores) __stcs(reinterpret_cast<uint4*>(out + (row0 + r) * H + c), rms_pack<T>(z));
+                        else *reinterpret_cast<uint4*>(out + (row0 + r) * H + c) = rms_pack<T>(z);
                     }
                 }
                 if (t == 0 && rstd_out != nullptr) rstd_out[row0 + r] = rstd;

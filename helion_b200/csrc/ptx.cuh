@@ -178,6 +178,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 // then dead) cannot push it out.
 enum L2Hint { kL2Normal = 0, kL2EvictFirst = 1, kL2EvictLast = 2 };
 
+__device__ __forceinline__ uint64_t make_l2_policy(int hint);
+
 // 1-D bulk copy global -> shared, no tensor map: both addresses 16-byte aligned and the size a multiple
 // of 16 bytes; completion is counted in bytes on `bar` like the tiled loads.
 __device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gmem_src, uint32_t bytes,
@@ -185,6 +187,14 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gmem
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void bulk_load_1d_hint(uint32_t smem_dst, const void* gmem_src, uint32_t bytes,
+                                                  uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
 }
 
