@@ -12,6 +12,9 @@
 // program and refuses next_pow2(V) > 131072).
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "row_kernels.cuh"
 
 namespace lce {
@@ -93,6 +96,80 @@ __device__ __forceinline__ void ce_fold(const float (&v)[PER], float& m, float& 
     m = nm;
 }
 
+// Fast fold of one whole in-range chunk straight from the raw 16-byte vectors of a 16-bit type: the chunk
+// maximum is taken on packed pairs (exact: the maximum of two 16-bit floats is one of them), each word is
+// split into its two values with one instruction each, and four independent chains sum the exponentials.
+// About 5 instructions per logit where the general path needs 16 (a capture of the forward on 4096 x 50304
+// bf16 showed it issue-bound at 0.82 instructions per scheduler cycle, not memory-bound). The order of the
+// additions is fixed, so the result is the same on every run.
+template <class T>
+__device__ __forceinline__ void ce_fold_raw16(const uint4 (&raw)[kCeVectors], float& m, float& s) {
+    static_assert(sizeof(T) == 2, "16-bit types");
+    constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+    unsigned w[4 * kCeVectors];
+#pragma unroll
+    for (int g = 0; g < kCeVectors; ++g) {
+        w[4 * g + 0] = raw[g].x;
+        w[4 * g + 1] = raw[g].y;
+        w[4 * g + 2] = raw[g].z;
+        w[4 * g + 3] = raw[g].w;
+    }
+    float cm;
+    if constexpr (kBf16) {
+        __nv_bfloat162 mx = *reinterpret_cast<const __nv_bfloat162*>(&w[0]);
+#pragma unroll
+        for (int i = 1; i < 4 * kCeVectors; ++i) mx = __hmax2(mx, *reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        cm = fmaxf(__low2float(mx), __high2float(mx));
+    } else {
+        __half2 mx = *reinterpret_cast<const __half2*>(&w[0]);
+#pragma unroll
+        for (int i = 1; i < 4 * kCeVectors; ++i) mx = __hmax2(mx, *reinterpret_cast<const __half2*>(&w[i]));
+        cm = fmaxf(__low2float(mx), __high2float(mx));
+    }
+    const float nm = fmaxf(m, cm);
+    const float nm2 = (nm == -INFINITY) ? 0.f : nm * kLog2e;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4 * kCeVectors; i += 2) {
+        float l0, h0, l1, h1;
+        if constexpr (kBf16) {  // a bf16 is the upper half of the float with the same value
+            l0 = __uint_as_float(w[i] << 16);
+            h0 = __uint_as_float(w[i] & 0xffff0000u);
+            l1 = __uint_as_float(w[i + 1] << 16);
+            h1 = __uint_as_float(w[i + 1] & 0xffff0000u);
+        } else {
+            const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&w[i + 1]));
+            l0 = p0.x;
+            h0 = p0.y;
+            l1 = p1.x;
+            h1 = p1.y;
+        }
+        a0 += ptx::ex2(fmaf(l0, kLog2e, -nm2));
+        a1 += ptx::ex2(fmaf(h0, kLog2e, -nm2));
+        a2 += ptx::ex2(fmaf(l1, kLog2e, -nm2));
+        a3 += ptx::ex2(fmaf(h1, kLog2e, -nm2));
+    }
+    s = s * ptx::ex2(fmaf(m, kLog2e, -nm2)) + ((a0 + a1) + (a2 + a3));
+    m = nm;
+}
+
+// The logit in register slot `slot` (0 .. kPerThread-1) of this thread, from the raw vectors.
+template <class T>
+__device__ __forceinline__ float ce_pick_raw(const uint4 (&raw)[kCeVectors], int slot) {
+    constexpr int VEC = CeTile<T>::kVec;
+    float out = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < kCeVectors; ++g) {
+        alignas(16) T tmp[VEC];
+        *reinterpret_cast<uint4*>(tmp) = raw[g];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j)
+            if (g * VEC + j == slot) out = Cvt<T>::to_f(tmp[j]);
+    }
+    return out;
+}
+
 // Index (0 .. kPerThread-1) of the register of THIS thread that holds column `target`, or -1.
 template <class T>
 __device__ __forceinline__ int ce_target_slot(long long col0, long long target) {
@@ -109,7 +186,7 @@ __device__ __forceinline__ int ce_target_slot(long long col0, long long target) 
 // FINAL (n_groups == 1): writes lse / loss_rows; else partial statistics
 // partial[(group*3 + c) * row_stride + row].
 template <class T, bool VECTOR, bool FINAL>
-__global__ void __launch_bounds__(kCeThreads, 4)
+__global__ void __launch_bounds__(kCeThreads, 3)
 ce_row_stats_kernel(const T* __restrict__ logits, const void* tgt, int tgt_i64, int N, long long V, int n_chunks,
                     int n_groups, float* __restrict__ partial, long long row_stride, long long ignore_index,
                     float* __restrict__ lse, float* __restrict__ loss_rows) {
@@ -132,6 +209,14 @@ ce_row_stats_kernel(const T* __restrict__ logits, const void* tgt, int tgt_i64, 
 #pragma unroll
         for (int g = 0; g < kCeVectors; ++g) cur[g] = next[g];
         if (c + 1 < c_end) ce_load_raw<T, VECTOR>(rowp, col0 + CeTile<T>::kChunk, V, next);
+        if constexpr (sizeof(T) == 2) {
+            if (col0 + CeTile<T>::kChunk <= V) {  // whole chunk in range (the same for every thread of the CTA)
+                ce_fold_raw16<T>(cur, m, s);
+                const int slot = ce_target_slot<T>(col0, target);
+                if (slot >= 0) t = ce_pick_raw<T>(cur, slot);  // at most one thread of the CTA, in one chunk
+                continue;
+            }
+        }
         float v[PER];
 #pragma unroll
         for (int g = 0; g < kCeVectors; ++g) {

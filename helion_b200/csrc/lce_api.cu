@@ -1597,7 +1597,7 @@ RmsShape rms_shape(long long H, int dtype, bool all_aligned, int n_streams = 1) 
 int rms_grid(const DeviceInfo& d, long long n_rows, int threads, long long cap) {
     // HELION_B200_RMS_GRID_MULT (tuning knob): grid = this many times the resident CTAs; 0 = one CTA per row
     // group, i.e. no persistence at all (the hardware deals the CTAs to the SMs as they retire)
-    static const int kGridMult = [] { const char* e = getenv("HELION_B200_RMS_GRID_MULT"); return e ? atoi(e) : 1; }();
+    static const int kGridMult = [] { const char* e = getenv("HELION_B200_RMS_GRID_MULT"); return e ? atoi(e) : 4; }();
     long long per_sm = 2048 / threads;
     if (per_sm > 16) per_sm = 16;
     long long g = static_cast<long long>(d.sm_count) * per_sm;
