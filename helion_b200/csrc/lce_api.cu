@@ -275,7 +275,7 @@ int choose_k_splits(long long M, long long Nn, long long K, int cg) {
     if (units == 0 || units * 2 > slots) return 1;
     long long s = slots / units;
     if (s > 16) s = 16;
-    while (s > 1 && (k_blocks / s < 8 || (s - 1) * cdiv(k_blocks, s) >= k_blocks)) --s;
+    while (s > 1 && (k_blocks / s < 16 || (s - 1) * cdiv(k_blocks, s) >= k_blocks)) --s;
     return static_cast<int>(s);
 }
 
