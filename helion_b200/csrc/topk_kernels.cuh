@@ -100,24 +100,62 @@ merge_topk_kernel(const float* __restrict__ partial, int n_tiles, int bn, long l
     }
 
     // ---- the k best of the tiles' candidates
-    for (int i = t; i < kTopkMaxK; i += kTopkThreads) keys[i] = 0ull;
+    // A bound first: the k-th largest of the tiles' maxima (record slot 0) is a lower bound of the k-th
+    // largest logit, because k tiles hold a logit at least that large. Only candidates that reach it can be
+    // among the k best - a few dozen to a few hundred of the n_tiles x kTileTop - so the main sort is small.
+    __shared__ int n_kept;
+    bool selected = false;
     const int total = n_tiles * kTileTop;
-    const int per_pass = kTopkSortN - kTopkMaxK;
-    for (int base = 0; base < total; base += per_pass) {
-        const int cnt = min(per_pass, total - base);
-        const int n = topk_pow2_at_least(kTopkMaxK + cnt);
+    if (n_tiles <= kTopkSortN) {
+        const int nt = topk_pow2_at_least(n_tiles);
+        for (int i = t; i < nt; i += kTopkThreads)
+            keys[i] = i < n_tiles ? topk_key(rec[static_cast<long long>(i) * kTopRecord * row_stride], 0) : 0ull;
+        topk_sort_desc(keys, nt);
+        const unsigned bound = n_tiles >= K ? static_cast<unsigned>(keys[K - 1] >> 32) : 0u;
         __syncthreads();
-        for (int i = t; i < n - kTopkMaxK; i += kTopkThreads) {
-            unsigned long long key = 0ull;
-            if (i < cnt) {
-                const int tile = (base + i) / kTileTop, slot = (base + i) % kTileTop;
-                const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+        if (t == 0) n_kept = 0;
+        __syncthreads();
+        for (int i = t; i < total; i += kTopkThreads) {
+            const int tile = i / kTileTop, slot = i % kTileTop;
+            const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+            const float val = r0[(2 + slot) * row_stride];
+            if (static_cast<unsigned>(topk_key(val, 0) >> 32) >= bound) {
                 const int col = __float_as_int(r0[(2 + kTileTop + slot) * row_stride]);
-                if (col >= 0) key = topk_key(r0[(2 + slot) * row_stride], col);
+                if (col >= 0) {
+                    const int pos = atomicAdd(&n_kept, 1);  // the order of arrival does not matter: sorted below
+                    if (pos < kTopkSortN) keys[pos] = topk_key(val, col);
+                }
             }
-            keys[kTopkMaxK + i] = key;
         }
-        topk_sort_desc(keys, n);
+        __syncthreads();
+        const int kept = n_kept;
+        if (kept <= kTopkSortN) {  // (else: too many equal values reach the bound - take the general path)
+            const int n = topk_pow2_at_least(kept);
+            for (int i = kept + t; i < n; i += kTopkThreads) keys[i] = 0ull;
+            topk_sort_desc(keys, n);
+            selected = true;
+        }
+    }
+    if (!selected) {  // general path: every candidate, kTopkSortN at a time together with the best so far
+        __syncthreads();
+        for (int i = t; i < kTopkMaxK; i += kTopkThreads) keys[i] = 0ull;
+        const int per_pass = kTopkSortN - kTopkMaxK;
+        for (int base = 0; base < total; base += per_pass) {
+            const int cnt = min(per_pass, total - base);
+            const int n = topk_pow2_at_least(kTopkMaxK + cnt);
+            __syncthreads();
+            for (int i = t; i < n - kTopkMaxK; i += kTopkThreads) {
+                unsigned long long key = 0ull;
+                if (i < cnt) {
+                    const int tile = (base + i) / kTileTop, slot = (base + i) % kTileTop;
+                    const float* r0 = rec + static_cast<long long>(tile) * kTopRecord * row_stride;
+                    const int col = __float_as_int(r0[(2 + kTileTop + slot) * row_stride]);
+                    if (col >= 0) key = topk_key(r0[(2 + slot) * row_stride], col);
+                }
+                keys[kTopkMaxK + i] = key;
+            }
+            topk_sort_desc(keys, n);
+        }
     }
 
     // ---- repair: tiles whose weakest kept entry still outranks the k-th key are recomputed in full.
