@@ -21,6 +21,7 @@ REDUCTIONS = {"none": REDUCTION_NONE, "mean": REDUCTION_MEAN, "sum": REDUCTION_S
 SIGNATURES = {
     "lce_version": (c_int, []),
     "lce_strerror": (c_char_p, [c_int]),
+    "lce_last_cuda_error": (c_char_p, []),
     "lce_launch_count": (ctypes.c_ulonglong, []),
     "lce_device_status": (c_int, [ctypes.POINTER(c_int), c_int]),
     "lce_forward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_uint]),
@@ -103,6 +104,8 @@ def lib() -> ctypes.CDLL:
 def check(code: int, what: str) -> None:
     if code != 0:
         msg = lib().lce_strerror(code).decode()
+        if code == 5:  # LCE_ERR_CUDA: say which CUDA error
+            msg += f" [{lib().lce_last_cuda_error().decode()}]"
         raise LceError(f"{what} failed: {msg} (code {code})")
 
 

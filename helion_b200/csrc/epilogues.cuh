@@ -298,9 +298,15 @@ struct EpiGrad {
         int row_off;            // first global row of the block
         long long col_global0;  // global vocab index of block column 0
         const float* lse;
-        const float* rowscale;
+        const float* rowscale;  // per-row factor, or nullptr: small batches derive it here (fields below)
         T* g;
         long long ldg;
+        // rowscale == nullptr: factor = grad_out (one float, or one per row) / valid-row count (mean only), 0 for
+        // ignored rows. Every epilogue warp counts the valid targets of all n_total rows itself - a few loads per
+        // lane while the tile's main loop runs - which saves small problems a launch.
+        const float* grad_out = nullptr;
+        int go_per_row = 0, mean = 0, n_total = 0;
+        long long ignore_index = -100;
     };
     struct State {
         float l2, sc;
@@ -311,12 +317,23 @@ struct EpiGrad {
         st.tcol = -1;
         st.sc = 0.f;
         st.l2 = 0.f;
+        float count = 1.f;
+        if (p.rowscale == nullptr && p.mean) {  // all 32 lanes of the warp take part
+            int c = 0;
+            for (int i = tc.row_in_tile & 31; i < p.n_total; i += 32) c += load_target(p.tgt, p.tgt_i64, i) != p.ignore_index;
+            count = static_cast<float>(__reduce_add_sync(0xffffffffu, c));
+        }
         if (st.row < p.rows) {
             const int grow = p.row_off + st.row;
-            st.sc = p.rowscale[grow];
+            const long long target = load_target(p.tgt, p.tgt_i64, grow);
+            if (p.rowscale != nullptr) {
+                st.sc = p.rowscale[grow];
+            } else if (target != p.ignore_index) {
+                const float g = p.go_per_row ? p.grad_out[grow] : p.grad_out[0];
+                st.sc = p.mean ? g / count : g;
+            }
             st.l2 = p.lse[grow] * kLog2e;
-            const long long rel = load_target(p.tgt, p.tgt_i64, grow) - p.col_global0 -
-                                  static_cast<long long>(tc.n_tile) * tc.bn;
+            const long long rel = target - p.col_global0 - static_cast<long long>(tc.n_tile) * tc.bn;
             if (rel >= 0 && rel < tc.bn) st.tcol = static_cast<int>(rel);
         }
     }

@@ -5,6 +5,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
@@ -43,6 +44,14 @@ std::mutex g_mutex;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 std::atomic<unsigned long long> g_launches{0};  // kernels this library has launched (all devices)
 #define LCE_COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
+
+// The CUDA error behind the last LCE_ERR_CUDA of this thread (lce_last_cuda_error reports its name).
+thread_local cudaError_t t_last_cuda_error = cudaSuccess;
+inline bool cuda_failed(cudaError_t e) {
+    if (e == cudaSuccess) return false;
+    t_last_cuda_error = e;
+    return true;
+}
 
 int device_info(DeviceInfo** out) {
     int dev = 0;
@@ -115,6 +124,10 @@ int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, lon
         *tm = slot.map;
         return LCE_OK;
     }
+    // The encoder is a DRIVER entry point and wants a context current on the calling thread. A thread that has
+    // made no runtime call yet (an autograd worker whose first CUDA call is this one) has none bound, and the
+    // encoder then fails with CUDA_ERROR_INVALID_CONTEXT; cudaFree(0) binds the device's primary context.
+    (void)cudaFree(nullptr);
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
     cuuint32_t box[2] = {box_inner, box_outer};
@@ -124,7 +137,13 @@ int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, lon
     const CUresult r = g_encode(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return LCE_ERR_CUDA;
+    if (r != CUDA_SUCCESS) {
+        t_last_cuda_error = static_cast<cudaError_t>(r);  // driver and runtime share the numbering of the common codes
+        if (getenv("HELION_B200_DEBUG"))
+            fprintf(stderr, "helion_b200: cuTensorMapEncodeTiled failed (%d): base %p inner %lld outer %lld pitch %lld box %u x %u\n",
+                    static_cast<int>(r), base, inner, outer, pitch_bytes, box_inner, box_outer);
+        return LCE_ERR_CUDA;
+    }
     slot.key = key;
     slot.map = *tm;
     slot.valid = true;
@@ -186,7 +205,7 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     // per kernel instantiation and device; setting the attribute twice from two threads is harmless
     static std::atomic<bool> smem_opted_in[kMaxDevices];
     if (!smem_opted_in[d.index].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cuda_failed(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
             return LCE_ERR_CUDA;
         smem_opted_in[d.index].store(true, std::memory_order_release);
     }
@@ -221,12 +240,12 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     // Long launches deal their tiles from a counter in the caller's workspace, zeroed in stream order here.
     const int dyn_waves = g_tuning.dyn_waves.load(std::memory_order_relaxed);
     int* counter = (sched != nullptr && dyn_waves > 0 && work >= dyn_waves * slots) ? sched : nullptr;
-    if (counter != nullptr && cudaMemsetAsync(counter, 0, sizeof(int), stream) != cudaSuccess) return LCE_ERR_CUDA;
+    if (counter != nullptr && cuda_failed(cudaMemsetAsync(counter, 0, sizeof(int), stream))) return LCE_ERR_CUDA;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
                                                raster, l2_hints, ep, d.status_ptr, counter);
     LCE_COUNT_LAUNCH();
-    return err == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
 
 // CTA pairs cover two 128-row tiles at a time; with an odd, small number of row tiles the second
@@ -318,7 +337,7 @@ int launch_simt(const DeviceInfo& d, const Mat& a, bool a_mn, const Mat& b, bool
     }
     if (!launched) gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(A, B, k, mt, nt, k_splits, ep);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -415,7 +434,7 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
             static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
             nullptr, tgt, tgt_i64, out.ignore_index, out.lse, out.loss_rows);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 // Greedy head: the forward GEMM with the argmax epilogue, then the per-row merge.
@@ -448,7 +467,7 @@ int greedy_head_impl(const DeviceInfo& d, const Path& path, const void* x, const
         static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), vocab_start,
         token, logprob, lse);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 // Sampling head: the forward GEMM with the top-candidates epilogue, then the per-row selection.
@@ -488,7 +507,7 @@ int topk_head_impl(const DeviceInfo& d, const Path& path, const void* x, const v
         static_cast<int>(N), static_cast<const T*>(x), static_cast<const T*>(w), static_cast<int>(H),
         static_cast<int>(V), scale, vocab_start, K, top_val, top_idx, lse);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -580,6 +599,9 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     return p;
 }
 
+// Small batches skip the rowscale launch: the recompute epilogue derives the per-row factor itself.
+inline bool fold_rowscale(long long N) { return N <= 1024; }
+
 int store_mode(long long idx, long long count) {
     if (count <= 1) return kStoreDirect;
     if (idx == 0) return kStoreFirst;
@@ -590,7 +612,8 @@ template <class T, class TDx>
 int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const void* x, const void* w,
                   const void* tgt, int tgt_i64, const float* lse, long long N, long long H, long long V,
                   long long vocab_start, void* dx, void* dw, char* ws, unsigned flags, void* const* dx_events,
-                  const lce_peer_scatter* scatter, float* dw_sumsq, cudaStream_t stream) {
+                  const lce_peer_scatter* scatter, float* dw_sumsq, const float* grad_out, int reduction,
+                  long long ignore_index, cudaStream_t stream) {
     const bool need_dx = !(flags & LCE_FLAG_NO_DX), need_dw = !(flags & LCE_FLAG_NO_DW);
     const bool use_tc = path.use_tc;
     const int cg = path.cg;
@@ -617,7 +640,12 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 ep.row_off = static_cast<int>(r0);
                 ep.col_global0 = vocab_start + c0;
                 ep.lse = lse;
-                ep.rowscale = rowscale;
+                ep.rowscale = fold_rowscale(N) ? nullptr : rowscale;
+                ep.grad_out = grad_out;
+                ep.go_per_row = reduction == LCE_REDUCTION_NONE ? 1 : 0;
+                ep.mean = reduction == LCE_REDUCTION_MEAN ? 1 : 0;
+                ep.n_total = static_cast<int>(N);
+                ep.ignore_index = ignore_index;
                 ep.g = g;
                 ep.ldg = p.ldg;
                 const Mat a{xp + r0 * H, nr, H, H}, b{wp + c0 * H, nc, H, H};
@@ -673,7 +701,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                         ep.scratch, splits, p.dx_slab_floats, m_tiles, n_tiles, bn, static_cast<int>(nr),
                         static_cast<int>(H), ep.out, H);
                     LCE_COUNT_LAUNCH();
-                    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+                    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
                 }
                 // rows r0.. of dX are final after the last band: let the caller start reducing them
                 // while the dW GEMM below (and later chunks) still run
@@ -720,7 +748,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                         ep.scratch, wsplits, p.dw_band_scratch_floats, m_tiles, n_tiles, bn, static_cast<int>(nc),
                         static_cast<int>(H), ep.out, H);
                     LCE_COUNT_LAUNCH();
-                    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+                    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
                 }
             }
         }
@@ -731,12 +759,12 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
         if (p.dw_splits > 1) {  // dW came out of the split-K reduction: one read of it, as lce_sumsq does
             sumsq_partial_kernel<T><<<kSumsqBlocks, kOptThreads, 0, stream>>>(static_cast<const T*>(dw), V * H, partials);
             LCE_COUNT_LAUNCH();
-            if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+            if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
             count = kSumsqBlocks;
         }
         sumsq_final_kernel<<<1, 1024, 0, stream>>>(partials, count, dw_sumsq, 0);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }
@@ -751,6 +779,8 @@ extern "C" {
 int lce_version(void) { return LCE_VERSION; }
 
 unsigned long long lce_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* lce_last_cuda_error(void) { return cudaGetErrorName(t_last_cuda_error); }
 
 void lce_set_tuning(int band_mb, int l2_hint_mode, int dyn_waves) {
     if (band_mb > 0) g_tuning.band_mb.store(band_mb, std::memory_order_relaxed);
@@ -909,14 +939,14 @@ int lce_finalize(const float* stats, int R, const void* target, int target_is_i6
         finalize_rows_kernel<<<static_cast<int>(cdiv(N, threads)), threads, 0, s>>>(
             stats, R, target, target_is_i64, static_cast<int>(N), ignore_index, lse, loss_rows);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     if (reduction != LCE_REDUCTION_NONE || valid_count) {
         reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, target, target_is_i64, static_cast<int>(N), ignore_index,
                                               reduction == LCE_REDUCTION_MEAN ? 1 : 0,
                                               reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }
@@ -975,7 +1005,7 @@ int lce_forward_loss(const void* x, const void* w, const void* target, int targe
                                               reduction == LCE_REDUCTION_MEAN ? 1 : 0,
                                               reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }
@@ -1047,22 +1077,25 @@ int lce_backward(const void* x, const void* w, const void* target, int target_is
     if (separate_count) {
         count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
-    rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
-        target, target_is_i64, static_cast<int>(N), ignore_index, grad_out,
-        reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0,
-        separate_count ? count : nullptr, rowscale);
-    LCE_COUNT_LAUNCH();
-    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    if (!fold_rowscale(N)) {
+        rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
+            target, target_is_i64, static_cast<int>(N), ignore_index, grad_out,
+            reduction == LCE_REDUCTION_NONE ? 1 : 0, reduction == LCE_REDUCTION_MEAN ? 1 : 0,
+            separate_count ? count : nullptr, rowscale);
+        LCE_COUNT_LAUNCH();
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
+    }
     const bool dx32 = (flags & LCE_FLAG_DX_F32) != 0;
     // the 256-byte head of the workspace holds the valid-row count (float 0) and the tile-deal counter (byte 128)
     const Path path{use_tc, cta_group_of(flags), reinterpret_cast<int*>(wsc + p.off_count + 128)};
 #define LCE_BWD(T)                                                                                          \
     (dx32 ? backward_impl<T, float>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, \
-                                    dx, dw, wsc, flags, dx_events, scatter, dw_sumsq, s)                    \
+                                    dx, dw, wsc, flags, dx_events, scatter, dw_sumsq, grad_out, reduction,     \
+                                    ignore_index, s)                                                        \
           : backward_impl<T, T>(*d, path, p, x, w, target, target_is_i64, lse, N, H, V, vocab_start, dx, \
-                                dw, wsc, flags, dx_events, nullptr, dw_sumsq, s))
+                                dw, wsc, flags, dx_events, nullptr, dw_sumsq, grad_out, reduction, ignore_index, s))
     switch (dtype) {
         case LCE_DTYPE_BF16: return LCE_BWD(__nv_bfloat16);
         case LCE_DTYPE_F16: return LCE_BWD(__half);
@@ -1210,7 +1243,7 @@ extern "C" int lce_dx_reduce_gather(const void* staging, int world, int rank, in
         default: return LCE_ERR_ARG;
     }
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 extern "C" int lce_dx_reduce_slice(const void* staging, int world, int rank, int64_t N, int64_t H, int dtype,
@@ -1236,7 +1269,7 @@ extern "C" int lce_dx_reduce_slice(const void* staging, int world, int rank, int
         default: return LCE_ERR_ARG;
     }
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1282,16 +1315,16 @@ int ce_forward_impl(const void* logits, const void* tgt, int tgt_i64, long long 
         if (vec) ce_row_stats_kernel<T, true, true><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
         else ce_row_stats_kernel<T, false, true><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
         LCE_COUNT_LAUNCH();
-        return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+        return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
     }
     if (vec) ce_row_stats_kernel<T, true, false><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
     else ce_row_stats_kernel<T, false, false><<<grid, kCeThreads, 0, s>>>(z, tgt, tgt_i64, (int)N, V, nc, ng, partial, l.row_stride, ignore_index, lse, loss_rows);
     LCE_COUNT_LAUNCH();
-    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     merge_partials_kernel<true><<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, s>>>(
         partial, ng, l.row_stride, static_cast<int>(N), nullptr, tgt, tgt_i64, ignore_index, lse, loss_rows);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 template <class T>
@@ -1303,7 +1336,7 @@ int ce_backward_impl(const void* logits, const void* tgt, int tgt_i64, long long
     if (vec) ce_backward_kernel<T, true><<<grid, kCeThreads, 0, s>>>(static_cast<const T*>(logits), tgt, tgt_i64, V, (int)n_chunks, lse, rowscale, static_cast<T*>(dlogits));
     else ce_backward_kernel<T, false><<<grid, kCeThreads, 0, s>>>(static_cast<const T*>(logits), tgt, tgt_i64, V, (int)n_chunks, lse, rowscale, static_cast<T*>(dlogits));
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 int check_ce_dims(long long N, long long V, int dtype, int reduction) {
@@ -1350,7 +1383,7 @@ int lce_ce_forward(const void* logits, const void* target, int target_is_i64, in
                                               reduction == LCE_REDUCTION_MEAN ? 1 : 0,
                                               reduction == LCE_REDUCTION_NONE ? nullptr : loss, valid_count);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }
@@ -1374,13 +1407,13 @@ int lce_ce_backward(const void* logits, const void* target, int target_is_i64, c
     if (separate_count) {
         count_valid_kernel<<<1, 1024, 0, s>>>(target, target_is_i64, static_cast<int>(N), ignore_index, count);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     rowscale_kernel<<<static_cast<int>(cdiv(N, 256)), 256, 0, s>>>(
         target, target_is_i64, static_cast<int>(N), ignore_index, grad_out, reduction == LCE_REDUCTION_NONE ? 1 : 0,
         reduction == LCE_REDUCTION_MEAN ? 1 : 0, separate_count ? count : nullptr, rowscale);
     LCE_COUNT_LAUNCH();
-    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     switch (dtype) {
         case LCE_DTYPE_BF16: return ce_backward_impl<__nv_bfloat16>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
         case LCE_DTYPE_F16: return ce_backward_impl<__half>(logits, target, target_is_i64, N, V, lse, rowscale, dlogits, s);
@@ -1443,7 +1476,7 @@ int matmul_impl(const DeviceInfo& d, const MatmulPlan& p, const Mat& a, bool a_m
             splitk_reduce_kernel<T><<<blocks, 256, 0, s>>>(ep.scratch, p.splits, p.slab_floats, m_tiles, n_tiles, kBN,
                                                           static_cast<int>(M), static_cast<int>(N), ep.out, ldc);
             LCE_COUNT_LAUNCH();
-            if (cudaGetLastError() != cudaSuccess) rc = LCE_ERR_CUDA;
+            if (cuda_failed(cudaGetLastError())) rc = LCE_ERR_CUDA;
         }
     }
     return rc;
@@ -1529,7 +1562,7 @@ int lce_adamw_step(void* param, const void* grad, float* exp_avg, float* exp_avg
             adamw_step_kernel<float><<<blocks, kOptThreads, 0, s>>>(static_cast<float*>(param), static_cast<const float*>(grad), exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
     }
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 size_t lce_sumsq_workspace_bytes(void) { return kSumsqBlocks * sizeof(float); }
@@ -1550,10 +1583,10 @@ int lce_sumsq(const void* x, int64_t n, int dtype, float* out, int accumulate, v
         default: sumsq_partial_kernel<float><<<kSumsqBlocks, kOptThreads, 0, s>>>(static_cast<const float*>(x), n, partials);
     }
     LCE_COUNT_LAUNCH();
-    if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     sumsq_final_kernel<<<1, 1024, 0, s>>>(partials, kSumsqBlocks, out, accumulate);
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 }  // extern "C"
@@ -1721,7 +1754,7 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
 #undef LCE_RMS_RING_FWD
             if (rc != LCE_OK) return rc;
             LCE_COUNT_LAUNCH();
-            return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+            return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
         }
     }
     const int grid = rms_grid(d, cdiv(n_rows, sh.rows), sh.threads, 0);
@@ -1746,7 +1779,7 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     }
 #undef LCE_RMS_FWD
     LCE_COUNT_LAUNCH();
-    return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
 }
 
 // Rows of partial dweight sums the backward writes for (n_rows, H): one per CTA of the row kernel.
@@ -1776,7 +1809,7 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
         float* rs = dweight != nullptr ? rstd_ws : nullptr;
         rms_backward_wide_kernel<T><<<grid, sh.threads, 0, s>>>(dyp, xp, wp, rstd, drp, dxp, rs, n, h, eps);
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
         if (dweight != nullptr) {
             n_partials = static_cast<int>(rms_partial_rows(n_rows, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16));
             const int rows_per_block = static_cast<int>(cdiv(n_rows, n_partials));
@@ -1784,7 +1817,7 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
             dim3 g(static_cast<unsigned>(cdiv(H, 256)), static_cast<unsigned>(n_partials));
             rms_dw_wide_kernel<T><<<g, 256, 0, s>>>(dyp, xp, rs, part, n, h, rows_per_block);
             LCE_COUNT_LAUNCH();
-            if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+            if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
         }
     } else if (RmsRingPlan rp; rms_backward_uses_ring(sh, H, sizeof(T) == 4 ? LCE_DTYPE_F32 : LCE_DTYPE_F16, drp != nullptr, &rp)) {
         const int grid = rms_ring_grid(d, sh, rp, n_rows, kRmsMaxPartials);
@@ -1813,7 +1846,7 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
 #undef LCE_RMS_RING_BWD
         if (rc != LCE_OK) return rc;
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     } else {
         const int grid = rms_grid(d, cdiv(n_rows, sh.rows), sh.threads, kRmsMaxPartials);
         n_partials = grid;
@@ -1836,14 +1869,14 @@ int rms_backward_launch(const DeviceInfo& d, const RmsShape& sh, const void* dy,
         }
 #undef LCE_RMS_BWD
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     if (dweight != nullptr) {
         dim3 block(32, 8);
         rms_dw_reduce_kernel<T><<<static_cast<unsigned>(cdiv(H, 32)), block, 0, s>>>(part, n_partials, h,
                                                                                      static_cast<T*>(dweight));
         LCE_COUNT_LAUNCH();
-        if (cudaGetLastError() != cudaSuccess) return LCE_ERR_CUDA;
+        if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
     }
     return LCE_OK;
 }

@@ -64,6 +64,9 @@ extern "C" {
 
 int lce_version(void);
 const char* lce_strerror(int code);
+/* Name of the CUDA error behind the calling thread's most recent LCE_ERR_CUDA from a kernel launch
+ * ("cudaSuccess" if there was none). */
+const char* lce_last_cuda_error(void);
 
 /* Number of kernels this library has launched since it was loaded (host-side counter, all devices
  * and streams). Lets a harness state how many of the library's own kernels ran inside a timed

@@ -417,3 +417,33 @@ def test_llama3_head_full_size_properties_and_memory():
     assert float(col_sum.abs().max()) <= 2e-2 * float(w.grad.float().abs().sum(dim=0).max())
     ignored = (t.view(-1) == -100)
     assert int(ignored.sum()) == 164 and float(x.grad.view(n, h)[ignored].abs().max()) == 0.0
+
+
+def test_first_cuda_call_of_a_fresh_thread_may_be_this_library():
+    """A thread that has made no CUDA runtime call yet (an autograd worker, a data-parallel thread) has no context
+    bound; the tensor-map encoder is a driver call and needs one. The library binds it itself."""
+    import threading
+
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(16, 512, generator=g).half().to(DEV)
+    w = torch.randn(1024, 512, generator=g).half().to(DEV)
+    t = torch.randint(0, 1024, (16,), generator=g).to(DEV)
+    ref = ops.linear_cross_entropy(x, w, t)
+    lse = torch.logsumexp(F.linear(x, w).float(), dim=-1)
+    torch.cuda.synchronize()
+    out = {}
+
+    def work():
+        try:
+            loss = ops.linear_cross_entropy(x, w, t)
+            dx, dw = ops.linear_cross_entropy_backward(torch.tensor(1.0, device=DEV), x, w, t, lse)
+            torch.cuda.synchronize()
+            out["ok"] = (float(loss), float(dx.float().abs().sum()), float(dw.float().abs().sum()))
+        except Exception as exc:  # noqa: BLE001
+            out["error"] = repr(exc)
+
+    th = threading.Thread(target=work)
+    th.start()
+    th.join()
+    assert "error" not in out, out
+    assert abs(out["ok"][0] - float(ref)) <= 1e-6 * abs(float(ref))
