@@ -21,12 +21,13 @@
 namespace lce {
 
 constexpr int kSimtBN = 128;
-constexpr int kSimtBK = 8;
+constexpr int kSimtBK = 16;
 constexpr int kSimtThreads = 256;
 constexpr int kSimtPitch = 128 + 4;   // operand tiles [k][mn] in floats: rows stay 16-byte aligned, the pad
                                       // spreads a k-contiguous deposit over the banks
 constexpr int kSimtCPitch = 64 + 4;   // one 64-column half of the C tile
-constexpr int kSimtLoads = 128 * kSimtBK / kSimtThreads;  // 4 elements of each operand per thread and k step
+constexpr int kSimtLoads = 128 * kSimtBK / kSimtThreads;  // 8 elements of each operand per thread and k step
+constexpr int kSimtVecs = kSimtLoads / 4;                  // = two 16-byte vectors for the vector loaders
 static_assert(kBM == 128, "the thread layout below is written for 128 x 128 tiles");
 
 template <class T>
@@ -53,6 +54,7 @@ struct SimtLoader;
 
 template <class T>
 struct SimtLoader<T, kSimtGeneric> {
+    static constexpr bool kAsync = false;
     const T* p;
     long long step, k_adv;
     int mn_t, k_t, mn_step, k_step, mn_left;
@@ -64,7 +66,7 @@ struct SimtLoader<T, kSimtGeneric> {
         k_adv = kSimtBK * op.stride_k;
         mn_left = op.extent_mn - mn0 - mn_t;  // element i is in range iff i * mn_step < mn_left
     }
-    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads], float*) {
 #pragma unroll
         for (int i = 0; i < kSimtLoads; ++i) {
             r[i] = 0.f;
@@ -80,31 +82,47 @@ struct SimtLoader<T, kSimtGeneric> {
 
 template <>
 struct SimtLoader<float, kSimtVecK> {
+    // thread t, vector i: row (t / (BK/4)) + i * (256 / (BK/4)), k offset 4 * (t % (BK/4))
+    static constexpr bool kAsync = false;
+    static constexpr int kPerRow = kSimtBK / 4;
+    static constexpr int kRowStep = kSimtThreads / kPerRow;
     const float* p;
+    long long row_adv;
     int row, k4;
-    bool valid;
+    bool valid[kSimtVecs];
     __device__ __forceinline__ void init(const SimtOperand<float>& op, int mn0, int k_begin, int t) {
-        row = t >> 1;
-        k4 = (t & 1) * 4;
-        valid = mn0 + row < op.extent_mn;
+        row = t / kPerRow;
+        k4 = (t % kPerRow) * 4;
+#pragma unroll
+        for (int i = 0; i < kSimtVecs; ++i) valid[i] = mn0 + row + i * kRowStep < op.extent_mn;
         p = op.ptr + static_cast<long long>(mn0 + row) * op.stride_mn + k_begin + k4;
+        row_adv = static_cast<long long>(kRowStep) * op.stride_mn;
     }
-    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid && k0 + k4 < k_end) v = *reinterpret_cast<const float4*>(p);  // K % 4 == 0: all four or none
-        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads], float*) {
+#pragma unroll
+        for (int i = 0; i < kSimtVecs; ++i) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid[i] && k0 + k4 < k_end) v = *reinterpret_cast<const float4*>(p + i * row_adv);  // K % 4 == 0: all four or none
+            r[4 * i + 0] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+        }
         p += kSimtBK;
     }
     __device__ __forceinline__ void deposit(float* tile, const float (&r)[kSimtLoads]) const {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tile[(k4 + j) * kSimtPitch + row] = r[j];
+        for (int i = 0; i < kSimtVecs; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tile[(k4 + j) * kSimtPitch + row + i * kRowStep] = r[4 * i + j];
     }
 };
 
 template <>
 struct SimtLoader<float, kSimtVecMN> {
+    // thread t, vector i: k (t / 32) + i * 8, m/n offset 4 * (t % 32). The tile in shared memory is [k][mn], so a
+    // 16-byte vector of consecutive m/n lands as it is: the copy goes global -> shared with cp.async and needs
+    // no registers between fetch and deposit (out-of-range vectors are zero-filled by a source size of 0).
+    static constexpr bool kAsync = true;
     const float* p;
-    long long k_adv;
+    long long k_adv, k_half;
     int k, mn4;
     bool valid;
     __device__ __forceinline__ void init(const SimtOperand<float>& op, int mn0, int k_begin, int t) {
@@ -113,16 +131,20 @@ struct SimtLoader<float, kSimtVecMN> {
         valid = mn0 + mn4 < op.extent_mn;  // extent % 4 == 0: all four or none
         p = op.ptr + (mn0 + mn4) + static_cast<long long>(k_begin + k) * op.stride_k;
         k_adv = kSimtBK * op.stride_k;
+        k_half = (kSimtThreads / 32) * op.stride_k;
+        if (!valid) p = op.ptr;  // never dereferenced (source size 0), but keep the address inside the tensor
     }
-    __device__ __forceinline__ void fetch(int k0, int k_end, float (&r)[kSimtLoads]) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid && k0 + k < k_end) v = *reinterpret_cast<const float4*>(p);
-        r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-        p += k_adv;
+    __device__ __forceinline__ void fetch(int k0, int k_end, float (&)[kSimtLoads], float* tile) {
+#pragma unroll
+        for (int i = 0; i < kSimtVecs; ++i) {
+            const bool in = valid && k0 + k + i * (kSimtThreads / 32) < k_end;
+            const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(tile + (k + i * (kSimtThreads / 32)) * kSimtPitch + mn4));
+            const float* src = in ? p + i * k_half : p;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(in ? 16 : 0) : "memory");
+        }
+        if (valid) p += k_adv;
     }
-    __device__ __forceinline__ void deposit(float* tile, const float (&r)[kSimtLoads]) const {
-        *reinterpret_cast<float4*>(tile + k * kSimtPitch + mn4) = make_float4(r[0], r[1], r[2], r[3]);
-    }
+    __device__ __forceinline__ void deposit(float*, const float (&)[kSimtLoads]) const {}
 };
 
 template <class T, class Epi, int AMODE = kSimtGeneric, int BMODE = kSimtGeneric>
@@ -136,7 +158,6 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
 
     const int t = threadIdx.x;
     const int ty = t >> 4, tx = t & 15;
-    static_assert(kSimtLoads == 4, "the vector loaders move one 16-byte vector per thread");
     // k_splits > 1: work item = (tile, slice of the contraction); the epilogue stores slices side by side
     // (kStoreSlice) and splitk_reduce_kernel adds them in slice order.
     const int total_tiles = m_tiles * n_tiles;
@@ -161,18 +182,21 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
         SimtLoader<T, BMODE> lb;
         la.init(A, m0, k_begin, t);
         lb.init(B, n0, k_begin, t);
+        constexpr bool kAnyAsync = SimtLoader<T, AMODE>::kAsync || SimtLoader<T, BMODE>::kAsync;
         float ra[kSimtLoads], rb[kSimtLoads];
-        la.fetch(k_begin, k_end, ra);
-        lb.fetch(k_begin, k_end, rb);
+        la.fetch(k_begin, k_end, ra, smem);
+        lb.fetch(k_begin, k_end, rb, smem + kTileFloats);
         la.deposit(smem, ra);
         lb.deposit(smem + kTileFloats, rb);
+        if constexpr (kAnyAsync) asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
         int cur = 0;
         for (int k0 = k_begin; k0 < k_end; k0 += kSimtBK) {
             const bool more = k0 + kSimtBK < k_end;
-            if (more) {  // in flight while this step multiplies
-                la.fetch(k0 + kSimtBK, k_end, ra);
-                lb.fetch(k0 + kSimtBK, k_end, rb);
+            float* nxt = smem + (cur ^ 1) * 2 * kTileFloats;
+            if (more) {  // in flight while this step multiplies (straight into the other buffer where the copy is async)
+                la.fetch(k0 + kSimtBK, k_end, ra, nxt);
+                lb.fetch(k0 + kSimtBK, k_end, rb, nxt + kTileFloats);
             }
             const float* As = smem + cur * 2 * kTileFloats;
             const float* Bs = As + kTileFloats;
@@ -190,9 +214,9 @@ gemm_simt_kernel(SimtOperand<T> A, SimtOperand<T> B, int K, int m_tiles, int n_t
                     for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
             }
             if (more) {
-                float* nxt = smem + (cur ^ 1) * 2 * kTileFloats;
                 la.deposit(nxt, ra);
                 lb.deposit(nxt + kTileFloats, rb);
+                if constexpr (kAnyAsync) asm volatile("cp.async.wait_all;" ::: "memory");
             }
             __syncthreads();
             cur ^= 1;
