@@ -162,7 +162,9 @@ struct Mat {
 //   hint_mode   L2 eviction hints: 0 none, 1 resident operand evict_last + streaming evict_first,
 //               2 evict_last only (HELION_B200_L2_HINTS)
 //   dyn_waves   launches of at least this many waves of tiles deal their tiles dynamically, when the caller's
-//               workspace has room for the counter; 0 = never (HELION_B200_DYN_WAVES)
+//               workspace has room for the counter; 0 = never (HELION_B200_DYN_WAVES). 32: the long forward
+//               launches, where the static deal drifts apart; the backward's launches are capped at about 28
+//               waves by the block size and measured 1 % faster on the static deal
 struct Tuning {
     std::atomic<int> band_mb, hint_mode, dyn_waves;
     Tuning() {
@@ -171,7 +173,7 @@ struct Tuning {
         e = getenv("HELION_B200_L2_HINTS");
         hint_mode = e ? atoi(e) : 2;
         e = getenv("HELION_B200_DYN_WAVES");
-        dyn_waves = e ? atoi(e) : 3;
+        dyn_waves = e ? atoi(e) : 32;
     }
 };
 Tuning g_tuning;

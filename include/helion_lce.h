@@ -304,7 +304,7 @@ int lce_rmsnorm_backward(const void* dy, const void* x, const void* weight, cons
 /* Tuning knobs of the tcgen05 launches, process-wide, for measurements: band_mb = MiB of operand panels the
  * tile order keeps resident in L2 (default 32), l2_hint_mode = 0 no eviction hints, 1 resident operand
  * evict_last + streaming operand evict_first, 2 evict_last only (default), dyn_waves = launches of at least
- * this many waves of tiles draw their tiles from a counter instead of round-robin (default 3, 0 = never).
+ * this many waves of tiles draw their tiles from a counter instead of round-robin (default 32, 0 = never).
  * A value that is out of range (band_mb <= 0, the others < 0) leaves that knob as it is. Results do not depend
  * on any of them. Test infrastructure like lce_debug_gemm. */
 void lce_set_tuning(int band_mb, int l2_hint_mode, int dyn_waves);
