@@ -25,6 +25,12 @@ def group_rank_size(process_group: Any) -> tuple[int, int]:
     return dist.get_rank(process_group), dist.get_world_size(process_group)
 
 
+def group_key(process_group: Any):
+    """A key for per-group caches: the group's unique name where torch gives it one (an ``id()`` can be handed
+    to a new group after the old one is gone), else the object's id."""
+    return getattr(process_group, "group_name", None) or id(process_group)
+
+
 def shard_bounds(vocab_size: int, world_size: int, rank: int) -> tuple[int, int]:
     """Rows ``[start, end)`` of the full weight that ``rank`` owns: equal contiguous shards, the last
     ranks one row shorter when the vocabulary does not divide evenly."""
@@ -198,7 +204,7 @@ def peer_buffers(process_group: Any, n_rows: int, hidden: int, device: torch.dev
     so variable-length batches neither leak symmetric memory nor rendezvous again. The decision to use the
     fused path is collective too (a MIN all-reduce over the group), so either every rank takes it or
     every rank takes the NCCL path."""
-    key = (id(process_group), hidden, device.index)
+    key = (group_key(process_group), hidden, device.index)
     have = _peer_buffers.get(key, False)
     if have is None:
         return None
@@ -229,7 +235,7 @@ def shard_start(process_group: Any, v_local: int, device: torch.device) -> int:
     rank, world = group_rank_size(process_group)
     if world == 1:
         return 0
-    key = (id(process_group), v_local)
+    key = (group_key(process_group), v_local)
     if key not in _shard_starts:
         import torch.distributed as dist
 
@@ -246,7 +252,7 @@ def ranks_agree(process_group: Any, key: tuple, values: tuple[int, ...], device:
     rank, world = group_rank_size(process_group)
     if world == 1:
         return True
-    full_key = (id(process_group),) + key
+    full_key = (group_key(process_group),) + key
     if full_key not in _agreements:
         import torch.distributed as dist
 
