@@ -126,8 +126,13 @@ int make_tmap(CUtensorMap* tm, const void* base, int dtype, long long inner, lon
     }
     // The encoder is a DRIVER entry point and wants a context current on the calling thread. A thread that has
     // made no runtime call yet (an autograd worker whose first CUDA call is this one) has none bound, and the
-    // encoder then fails with CUDA_ERROR_INVALID_CONTEXT; cudaFree(0) binds the device's primary context.
-    (void)cudaFree(nullptr);
+    // encoder then fails with CUDA_ERROR_INVALID_CONTEXT. cudaSetDevice on the thread's current device binds
+    // the primary context (and, unlike cudaFree(0), is no stream operation, so it is legal under stream capture).
+    {
+        static thread_local int bound_device = -1;
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev != bound_device && cudaSetDevice(dev) == cudaSuccess) bound_device = dev;
+    }
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
     cuuint32_t box[2] = {box_inner, box_outer};

@@ -447,3 +447,33 @@ def test_first_cuda_call_of_a_fresh_thread_may_be_this_library():
     th.join()
     assert "error" not in out, out
     assert abs(out["ok"][0] - float(ref)) <= 1e-6 * abs(float(ref))
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The op only enqueues work on the caller's stream (kernels and 4-byte memsets), so a forward + backward can
+    be captured into a CUDA graph after a warm-up call and replayed on new data in the same buffers."""
+    g = torch.Generator().manual_seed(22)
+    n, h, v = 512, 256, 40000  # long enough for the dynamic tile deal (its counter memset is captured too)
+    x = torch.randn(n, h, generator=g).bfloat16().to(DEV).requires_grad_(True)
+    w = (torch.randn(v, h, generator=g) * 0.05).bfloat16().to(DEV).requires_grad_(True)
+    t = torch.randint(0, v, (n,), generator=g).to(DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # warm-up outside the capture (allocations, attribute calls, tensor maps)
+            x.grad = w.grad = None
+            ops.linear_cross_entropy(x, w, t).backward()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    x.grad = w.grad = None
+    with torch.cuda.graph(graph):
+        loss = ops.linear_cross_entropy(x, w, t)
+        loss.backward()
+    with torch.no_grad():
+        x.copy_(torch.randn(n, h, generator=g).bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    ref = oracle.expression(x.detach().cpu(), w.detach().cpu(), t.cpu())
+    assert rel_loss_err(loss, ref["loss"]) <= LOSS_RTOL
+    assert scaled_max_err(x.grad, ref["dx"]) <= GRAD_RTOL_16BIT
+    assert scaled_max_err(w.grad, ref["dw"]) <= GRAD_RTOL_16BIT
