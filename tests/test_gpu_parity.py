@@ -477,3 +477,64 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
     assert rel_loss_err(loss, ref["loss"]) <= LOSS_RTOL
     assert scaled_max_err(x.grad, ref["dx"]) <= GRAD_RTOL_16BIT
     assert scaled_max_err(w.grad, ref["dw"]) <= GRAD_RTOL_16BIT
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_dx_reduce_scatter_emulated_on_one_gpu(world):
+    """The vocabulary-parallel dX reduction, with the ranks played one after the other on ONE GPU (no kernel of
+    the library waits on another rank, so the order does not matter): every rank's dX GEMM scatters its partial
+    rows through the peer-store epilogue into the owners' staging buffers (here: local buffers), each owner sums
+    its slice (`lce_dx_reduce_slice`) - and, the older form, sums and stores into every rank's final buffer
+    (`lce_dx_reduce_gather`). Both must reproduce the unsharded dX; the local dW blocks the unsharded dW."""
+    import ctypes
+
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(30 + world)
+    n, h, v = 1000, 256, world * 1002 + 5  # token count not a multiple of world * 128, uneven shards
+    x = torch.randn(n, h, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(v, h, generator=g) * 0.08).bfloat16().to(DEV)
+    t = torch.randint(0, v, (n,), generator=g).to(DEV)
+    t[::13] = -100
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    loss = ops.linear_cross_entropy(xr, wr, t)
+    loss.backward(torch.tensor(1.7, device=DEV))
+    lse = torch.logsumexp(F.linear(x.float(), w.float()), dim=-1)
+    go = torch.tensor(1.7, device=DEV)
+    rpr = -(-n // world)
+    staging = [torch.full((world, rpr, h), float("nan"), device=DEV) for _ in range(world)]
+    code = _lib.DTYPE_BF16
+    flags = _lib.FLAG_DX_F32
+    from helion_b200 import parallel
+
+    dws = []
+    for r in range(world):
+        start, end = parallel.shard_bounds(v, world, r)
+        w_r = w[start:end].contiguous()
+        dw_r = torch.empty_like(w_r)
+        scatter = _lib.PeerScatter()
+        for k in range(world):
+            scatter.staging[k] = staging[k].data_ptr()
+        scatter.rank, scatter.world = r, world
+        ws = torch.empty(L.lce_backward_workspace_bytes(n, h, end - start, code, flags, 0), dtype=torch.uint8, device=DEV)
+        _lib.check(L.lce_backward(x.data_ptr(), w_r.data_ptr(), t.data_ptr(), 1, lse.data_ptr(), go.data_ptr(), n, h,
+                                  end - start, start, code, -100, _lib.REDUCTION_MEAN, None, dw_r.data_ptr(), ws.data_ptr(),
+                                  ws.numel(), flags, 0, None, ctypes.byref(scatter), None,
+                                  torch.cuda.current_stream().cuda_stream), "lce_backward")
+        dws.append(dw_r)
+    torch.cuda.synchronize()
+    pieces = []
+    finals = [torch.zeros(n, h, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    out_ptrs = (ctypes.c_void_p * world)(*[f.data_ptr() for f in finals])
+    for r in range(world):
+        piece = torch.zeros(rpr, h, dtype=torch.bfloat16, device=DEV)
+        _lib.check(L.lce_dx_reduce_slice(staging[r].data_ptr(), world, r, n, h, code, piece.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream), "lce_dx_reduce_slice")
+        _lib.check(L.lce_dx_reduce_gather(staging[r].data_ptr(), world, r, n, h, code, out_ptrs,
+                                          torch.cuda.current_stream().cuda_stream), "lce_dx_reduce_gather")
+        pieces.append(piece)
+    torch.cuda.synchronize()
+    dx = torch.cat(pieces)[:n]
+    assert scaled_max_err(dx, xr.grad.float()) <= 8e-3
+    assert all(torch.equal(f, dx) for f in finals)
+    assert scaled_max_err(torch.cat(dws), wr.grad.float()) <= 8e-3
+    assert _lib.device_status() == 0
