@@ -211,6 +211,10 @@ def peer_buffers(process_group: Any, n_rows: int, hidden: int, device: torch.dev
     if have is False or have.capacity_rows < n_rows:
         import torch.distributed as dist
 
+        if have is not False:
+            # a smaller pair is being replaced: nothing on this GPU or its peers may still be writing into it
+            torch.cuda.synchronize(device)
+            dist.barrier(group=process_group)
         _peer_buffers.pop(key, None)  # drop the smaller pair before its replacement is allocated
         del have
         try:

@@ -46,7 +46,9 @@ def cases_for(world: int):
                 ("14b-class", dict(rows=2100, hidden=256, vocab=8 * 594 + 5), "sum", False)]
     return [("llama3-8b", dict(rows=640, hidden=512, vocab=4 * 1002), "mean", True),
             ("14b-class", dict(rows=1536, hidden=256, vocab=4 * 594), "sum", True),
-            ("large-vocab", dict(rows=500, hidden=384, vocab=4 * 1002 + 3), "mean", False)]
+            ("large-vocab", dict(rows=500, hidden=384, vocab=4 * 1002 + 3), "mean", False),
+            # same hidden size as the first case with more rows: the cached peer buffers must grow, collectively
+            ("llama3-8b", dict(rows=900, hidden=512, vocab=4 * 1002), "sum", True)]
 
 
 def _worker(rank: int, world: int, port: int, results, dx_reduce: str) -> None:
