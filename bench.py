@@ -54,7 +54,7 @@ class ClockSampler:
     """Samples SM clock, power and throttle reasons through NVML every few milliseconds while the timed
     region runs (read-only queries; nothing on the GPU is changed)."""
 
-    def __init__(self, gpu_index: int, period_s: float = 0.004):
+    def __init__(self, gpu_index: int, period_s: float = 0.005):
         self.gpu_index = gpu_index
         self.period_s = period_s
         self.samples: list[tuple[int, float, int]] = []
@@ -91,6 +91,11 @@ class ClockSampler:
                 self.error = str(exc)
                 return
             time.sleep(self.period_s)
+
+    def mark(self) -> None:
+        """Forget what was sampled so far: the region of interest starts now. Starting the sampler well before
+        that region keeps NVML's start-up and its first, slow queries out of it."""
+        self.samples = []
 
     def stop(self) -> dict:
         if self._thread is None:
@@ -276,6 +281,8 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         loss = step(x, t)
     barrier()
+    sampler = ClockSampler(local)
+    sampler.start()  # every rank samples its own GPU; started here so that NVML's start-up is over by the timed region
     preheat_steps = 0
     t_heat = time.perf_counter()
     while args.preheat_s > 0:
@@ -289,11 +296,10 @@ def run_ours(args) -> None:
         if float(go_on.item()) == 0.0:
             break
     preheat_s = time.perf_counter() - t_heat
-    sampler = ClockSampler(local)
-    sampler.start()  # every rank samples its own GPU
     launches0 = L.lce_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark()
     e0.record()
     for _ in range(args.steps):
         loss = step(x, t)
@@ -404,9 +410,10 @@ def run_ours(args) -> None:
     # (best of ten 0.7 ms GEMMs on an idle GPU); K launches back to back each time, average duration.
     ms_fwd_hot = time_fwd_kernel()
     barrier()
-    time.sleep(args.rest_s)
     rest_sampler = ClockSampler(local)
     rest_sampler.start()
+    time.sleep(args.rest_s)
+    rest_sampler.mark()
     ms_fwd = time_fwd_kernel()
     rest_clocks = rest_sampler.stop()
 
