@@ -56,6 +56,53 @@ __device__ __forceinline__ void store_row32(T* dst, const float (&v)[32], int nc
     }
 }
 
+// Line-wide stores of 16-bit results. A thread owns one row and receives it 32 columns at a time; stored
+// directly, every store instruction touches 32 rows with 16 bytes each - 32 partial-sector requests, which
+// is what bounds a GEMM with a short contraction (the output is large, the main loop short). Here the warp
+// parks two consecutive chunks (64 columns = 128 bytes per row) in its shared-memory area and then writes
+// whole 128-byte lines: 8 lanes per row, 4 rows per store instruction.
+// Area layout: [32 rows][8 pieces of 16 bytes], the piece index XORed with the row's low three bits, so the
+// row-wise deposit and the line-wise pick-up are both free of bank conflicts.
+// All 32 lanes call this for every chunk of the tile, in column order; half = (col0 / 32) & 1.
+//   out_blk     address of (first row of this warp, first column of the 64-column block), 16-byte aligned
+//   ld          row pitch in elements, a multiple of 8
+//   rows_valid  how many of the warp's 32 rows exist (<= 0: none)
+//   cols_valid  how many of the block's 64 columns exist (<= 0: none)
+template <class T>
+__device__ __forceinline__ void store_block64(float* stage, int lane, int half, const float (&v)[32], T* out_blk,
+                                              long long ld, int rows_valid, int cols_valid) {
+    static_assert(sizeof(T) == 2, "16-bit outputs only");
+    uint4* sm = reinterpret_cast<uint4*>(stage);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        alignas(16) T tmp[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tmp[j] = Cvt<T>::from_f(v[i * 8 + j]);
+        sm[lane * 8 + ((half * 4 + i) ^ (lane & 7))] = *reinterpret_cast<const uint4*>(tmp);
+    }
+    if (half == 0) return;
+    __syncwarp();
+    const int piece = lane & 7;
+    const int left = cols_valid - piece * 8;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const uint4 val = sm[r * 8 + (piece ^ (r & 7))];
+        if (r < rows_valid && left > 0) {
+            T* dst = out_blk + static_cast<long long>(r) * ld + piece * 8;
+            if (left >= 8) {
+                *reinterpret_cast<uint4*>(dst) = val;
+            } else {
+                const T* e = reinterpret_cast<const T*>(&val);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < left) dst[j] = e[j];
+            }
+        }
+    }
+    __syncwarp();  // the area is free again
+}
+
 // ---------------------------------------------------------------------------------------------
 // Forward: per (vocab tile, row) partial softmax statistics.
 //   partial[(n_tile*3 + 0) * row_stride + row] = max_j z[row, j]
@@ -307,6 +354,7 @@ struct EpiGrad {
         const float* grad_out = nullptr;
         int go_per_row = 0, mean = 0, n_total = 0;
         long long ignore_index = -100;
+        int wide = 0;  // 16-bit G leaves as whole 128-byte lines (store_block64) where the core provides the area
     };
     struct State {
         float l2, sc;
@@ -339,9 +387,10 @@ struct EpiGrad {
     }
     static __device__ __forceinline__ void chunk(State& st, const Params& p, const TileCtx& tc,
                                                  int col0, float (&v)[32]) {
-        if (st.row >= p.rows) return;
         const int bcol0 = tc.n_tile * tc.bn + col0;  // column inside the block
-        if (bcol0 >= p.cols) return;
+        bool wide = false;
+        if constexpr (sizeof(T) == 2) wide = p.wide != 0 && tc.stage != nullptr;
+        if (!wide && (st.row >= p.rows || bcol0 >= p.cols)) return;
         if (st.sc == 0.f) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -352,6 +401,15 @@ struct EpiGrad {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     if (col0 + j == st.tcol) v[j] -= st.sc;
+            }
+        }
+        if constexpr (sizeof(T) == 2) {
+            if (wide) {  // all 32 lanes, rows or columns past the end included (nothing is stored for those)
+                const int lane = tc.row_in_tile & 31, half = (col0 >> 5) & 1;
+                const int row_base = st.row - lane, blk0 = bcol0 - half * 32;
+                store_block64<T>(tc.stage, lane, half, v, p.g + static_cast<long long>(row_base) * p.ldg + blk0, p.ldg,
+                                 p.rows - row_base, p.cols - blk0);
+                return;
             }
         }
         store_row32<T>(p.g + static_cast<long long>(st.row) * p.ldg + bcol0, v, p.cols - bcol0);
@@ -403,6 +461,9 @@ struct EpiStore {
         // so the total is the same on every run. nullptr = off. Only in the modes that produce final values.
         float* sumsq_partial = nullptr;
         int sumsq_tile0 = 0;
+        // 16-bit results leave as whole 128-byte lines (store_block64). The host sets it only when `out` is
+        // 16-byte aligned and ldo is a multiple of 8.
+        int wide = 0;
     };
     struct State {
         int row;
@@ -470,6 +531,23 @@ struct EpiStore {
                     }
                 }
                 __syncwarp();
+                return;
+            }
+        }
+        if constexpr (sizeof(T) == 2) {
+            if (p.wide != 0 && tc.stage != nullptr) {  // all 32 lanes take part, whatever their row and column
+                const int lane = tc.row_in_tile & 31, half = (col0 >> 5) & 1;
+                const int row_base = st.row - lane, blk0 = gcol0 - half * 32;
+                store_block64<T>(tc.stage, lane, half, v, p.out + static_cast<long long>(row_base) * p.ldo + blk0, p.ldo,
+                                 p.rows - row_base, p.cols - blk0);
+                if (p.sumsq_partial != nullptr && st.row < p.rows) {
+                    const int valid = p.cols - gcol0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float r = Cvt<T>::to_f(Cvt<T>::from_f(v[j]));  // the value as stored
+                        if (j < valid) st.sq = fmaf(r, r, st.sq);
+                    }
+                }
                 return;
             }
         }

@@ -192,6 +192,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (kPair) ptx::cluster_sync_all();  // the peer's barriers exist before anyone signals them
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    // Everything above touched no global memory. From here on the kernel reads what its predecessor in the
+    // stream wrote (operands, row factors, the tile counter): wait for it, and let the successor begin its own
+    // set-up now (it waits the same way before it reads anything of ours).
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
 
     // Reader side of the tile deal: the work item that follows the `seq`-th one this CTA handled.
     // Static deal: the next one round-robin. Dynamic deal: what the leader's producer put into ring slot
@@ -395,12 +400,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             ptx::tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            // two chunks in flight: the tensor-memory read of the next chunk runs under the work on this one
+            static_assert((BN / 32) % 2 == 0, "chunks are taken in pairs");
+            float va[32], vb[32];
+            ptx::tmem_ld_32x32(taddr, va);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                ptx::tmem_ld_32x32(taddr + c * 32, v);
+            for (int c = 0; c < BN / 32; c += 2) {
                 ptx::tmem_ld_wait();
-                Epi::chunk(st, ep, tc, c * 32, v);
+                ptx::tmem_ld_32x32(taddr + (c + 1) * 32, vb);
+                Epi::chunk(st, ep, tc, c * 32, va);
+                ptx::tmem_ld_wait();
+                if (c + 2 < BN / 32) ptx::tmem_ld_32x32(taddr + (c + 2) * 32, va);
+                Epi::chunk(st, ep, tc, (c + 1) * 32, vb);
             }
             // all TMEM reads of this buffer are done: hand it back to the MMA issuer
             ptx::tc_fence_before_sync();

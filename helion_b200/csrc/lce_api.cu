@@ -183,6 +183,30 @@ struct Tuning {
 };
 Tuning g_tuning;
 
+// Programmatic dependent launch (HELION_B200_PDL=0 switches it off): kernels that call ptx::grid_dep_wait()
+// before they read anything their predecessor in the stream wrote may be launched while that predecessor is
+// still running; their launch latency and set-up then hide under its tail.
+inline bool pdl_enabled() {
+    static const bool kEnabled = [] { const char* e = getenv("HELION_B200_PDL"); return e ? atoi(e) != 0 : true; }();
+    return kEnabled;
+}
+
+// Launches such a kernel (no dynamic shared memory). Only for kernels that contain the wait.
+template <class... KArgs, class... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), int grid, int block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
                  int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream, int* sched) {
@@ -224,13 +248,24 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CG;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    // The kernel waits for its predecessor in the stream itself (ptx::grid_dep_wait after its set-up), so it may
+    // be started under the predecessor's tail; pairs additionally launch as clusters of two.
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (CG > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = CG;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = CG > 1 ? 1 : 0;
+    cfg.numAttrs = n_attr;
     // the banded operand is re-read by every tile of the band: keep it; the other one streams
     const int stream_hint = kHintMode == 1 ? ptx::kL2EvictFirst : ptx::kL2Normal;
     const int l2_hints = kHintMode == 0 ? 0 : (m_fastest ? (ptx::kL2EvictLast | (stream_hint << 2))
@@ -428,20 +463,22 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
     }
     if (rc) return rc;
     const int blocks = static_cast<int>(cdiv(N, kMergeRows)), threads = kMergeRows * kMergeLanes;
+    cudaError_t err;
     if (out.one_launch_tail)
-        merge_finalize_small_kernel<<<1, 1024, 0, stream>>>(
-            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), tgt, tgt_i64,
-            out.ignore_index, out.reduction, out.lse, out.loss, out.valid_count);
+        err = launch_dependent(merge_finalize_small_kernel, 1, 1024, stream,
+                               static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
+                               tgt, tgt_i64, out.ignore_index, out.reduction, out.lse, out.loss, out.valid_count);
     else if (out.stats != nullptr)
-        merge_partials_kernel<false><<<blocks, threads, 0, stream>>>(
-            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
-            out.stats, nullptr, 0, 0, nullptr, nullptr);
+        err = launch_dependent(merge_partials_kernel<false>, blocks, threads, stream,
+                               static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
+                               out.stats, static_cast<const void*>(nullptr), 0, 0ll, static_cast<float*>(nullptr),
+                               static_cast<float*>(nullptr));
     else
-        merge_partials_kernel<true><<<blocks, threads, 0, stream>>>(
-            static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
-            nullptr, tgt, tgt_i64, out.ignore_index, out.lse, out.loss_rows);
+        err = launch_dependent(merge_partials_kernel<true>, blocks, threads, stream,
+                               static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N),
+                               static_cast<float*>(nullptr), tgt, tgt_i64, out.ignore_index, out.lse, out.loss_rows);
     LCE_COUNT_LAUNCH();
-    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
+    return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
 
 // Greedy head: the forward GEMM with the argmax epilogue, then the per-row merge.
@@ -470,11 +507,12 @@ int greedy_head_impl(const DeviceInfo& d, const Path& path, const void* x, const
         rc = launch_simt<T, EpiTop1>(d, a, false, b, false, N, V, H, ep, stream);
     }
     if (rc) return rc;
-    merge_top1_kernel<<<static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, 0, stream>>>(
+    const cudaError_t err = launch_dependent(
+        merge_top1_kernel, static_cast<int>(cdiv(N, kMergeRows)), kMergeRows * kMergeLanes, stream,
         static_cast<const float*>(ws), static_cast<int>(l.n_tiles), l.row_stride, static_cast<int>(N), vocab_start,
         token, logprob, lse);
     LCE_COUNT_LAUNCH();
-    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
+    return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
 
 // Sampling head: the forward GEMM with the top-candidates epilogue, then the per-row selection.
@@ -509,12 +547,13 @@ int topk_head_impl(const DeviceInfo& d, const Path& path, const void* x, const v
         rc = launch_simt<T, EpiTopK>(d, a, false, b, false, N, V, H, ep, stream);
     }
     if (rc) return rc;
-    merge_topk_kernel<T><<<static_cast<int>(N), kTopkThreads, 0, stream>>>(
+    const cudaError_t err = launch_dependent(
+        merge_topk_kernel<T>, static_cast<int>(N), kTopkThreads, stream,
         static_cast<const float*>(ws), static_cast<int>(l.n_tiles), use_tc ? kBN : kSimtBN, l.row_stride,
         static_cast<int>(N), static_cast<const T*>(x), static_cast<const T*>(w), static_cast<int>(H),
         static_cast<int>(V), scale, vocab_start, K, top_val, top_idx, lse);
     LCE_COUNT_LAUNCH();
-    return (cuda_failed(cudaGetLastError()) ? LCE_ERR_CUDA : LCE_OK);
+    return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -606,6 +645,13 @@ BwdPlan plan_backward(long long N, long long H, long long V, int dtype, bool use
     return p;
 }
 
+// Whether a 16-bit result may leave the tcgen05 epilogue as whole 128-byte lines (store_block64): needs 16-byte
+// aligned rows. HELION_B200_EPI_WIDE=0 (tuning knob) switches back to per-thread row stores.
+inline int wide_stores(const void* out, long long ld) {
+    static const int kEnabled = [] { const char* e = getenv("HELION_B200_EPI_WIDE"); return e ? atoi(e) : 1; }();
+    return (kEnabled != 0 && aligned16(out) && ld % 8 == 0) ? 1 : 0;
+}
+
 // Small batches skip the rowscale launch: the recompute epilogue derives the per-row factor itself.
 inline bool fold_rowscale(long long N) { return N <= 1024; }
 
@@ -655,6 +701,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 ep.ignore_index = ignore_index;
                 ep.g = g;
                 ep.ldg = p.ldg;
+                ep.wide = wide_stores(g, p.ldg);
                 const Mat a{xp + r0 * H, nr, H, H}, b{wp + c0 * H, nc, H, H};
                 if (use_tc) {
                     if constexpr (sizeof(T) == 2)
@@ -677,6 +724,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 ep.mode = store_mode(cb, p.n_cblk);
                 ep.slab_floats = p.dx_slab_floats;
                 ep.peer_world = 0;
+                ep.wide = wide_stores(ep.out, H);
                 if constexpr (std::is_same<TDx, float>::value) {
                     if (scatter != nullptr) {  // finished rows go straight to the GPUs that own them
                         ep.peer_world = scatter->world;
@@ -704,11 +752,11 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                     const int m_tiles = static_cast<int>(cdiv(nr, kBM)), n_tiles = static_cast<int>(cdiv(H, bn));
                     const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
                     const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
-                    splitk_reduce_kernel<TDx><<<blocks, 256, 0, stream>>>(
-                        ep.scratch, splits, p.dx_slab_floats, m_tiles, n_tiles, bn, static_cast<int>(nr),
-                        static_cast<int>(H), ep.out, H);
+                    const cudaError_t err = launch_dependent(
+                        splitk_reduce_kernel<TDx>, blocks, 256, stream, static_cast<const float*>(ep.scratch), splits,
+                        p.dx_slab_floats, m_tiles, n_tiles, bn, static_cast<int>(nr), static_cast<int>(H), ep.out, H);
                     LCE_COUNT_LAUNCH();
-                    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
+                    if (cuda_failed(err)) return LCE_ERR_CUDA;
                 }
                 // rows r0.. of dX are final after the last band: let the caller start reducing them
                 // while the dW GEMM below (and later chunks) still run
@@ -727,6 +775,7 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 ep.mode = store_mode(rb, p.n_rblk);
                 ep.slab_floats = p.dw_band_scratch_floats;
                 ep.peer_world = 0;
+                ep.wide = wide_stores(ep.out, H);
                 if (dw_sumsq != nullptr && p.dw_splits == 1) {  // gradient-norm partials ride on the final stores
                     ep.sumsq_partial = reinterpret_cast<float*>(ws + p.off_sumsq);
                     ep.sumsq_tile0 = static_cast<int>(c0 / kBM);
@@ -751,11 +800,11 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                     const int m_tiles = static_cast<int>(cdiv(nc, kBM)), n_tiles = static_cast<int>(cdiv(H, bn));
                     const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
                     const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
-                    splitk_reduce_kernel<T><<<blocks, 256, 0, stream>>>(
-                        ep.scratch, wsplits, p.dw_band_scratch_floats, m_tiles, n_tiles, bn, static_cast<int>(nc),
-                        static_cast<int>(H), ep.out, H);
+                    const cudaError_t err = launch_dependent(
+                        splitk_reduce_kernel<T>, blocks, 256, stream, static_cast<const float*>(ep.scratch), wsplits,
+                        p.dw_band_scratch_floats, m_tiles, n_tiles, bn, static_cast<int>(nc), static_cast<int>(H), ep.out, H);
                     LCE_COUNT_LAUNCH();
-                    if (cuda_failed(cudaGetLastError())) return LCE_ERR_CUDA;
+                    if (cuda_failed(err)) return LCE_ERR_CUDA;
                 }
             }
         }
@@ -1466,6 +1515,7 @@ int matmul_impl(const DeviceInfo& d, const MatmulPlan& p, const Mat& a, bool a_m
     ep.mode = p.splits > 1 ? kStoreSlice : kStoreDirect;
     ep.slab_floats = p.slab_floats;
     ep.peer_world = 0;
+    ep.wide = wide_stores(c, ldc);
     if (!p.use_tc) return launch_simt<T, EpiStore<T>>(d, a, a_mn, b, b_mn, M, N, K, ep, s);
     int rc = LCE_ERR_ARG;
     if constexpr (sizeof(T) == 2) {
@@ -1480,10 +1530,11 @@ int matmul_impl(const DeviceInfo& d, const MatmulPlan& p, const Mat& a, bool a_m
             const int m_tiles = static_cast<int>(cdiv(M, kBM)), n_tiles = static_cast<int>(cdiv(N, kBN));
             const long long quads = static_cast<long long>(m_tiles) * n_tiles * (kBN / 4) * kBM;
             const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
-            splitk_reduce_kernel<T><<<blocks, 256, 0, s>>>(ep.scratch, p.splits, p.slab_floats, m_tiles, n_tiles, kBN,
-                                                          static_cast<int>(M), static_cast<int>(N), ep.out, ldc);
+            const cudaError_t err = launch_dependent(
+                splitk_reduce_kernel<T>, blocks, 256, s, static_cast<const float*>(ep.scratch), p.splits, p.slab_floats,
+                m_tiles, n_tiles, static_cast<int>(kBN), static_cast<int>(M), static_cast<int>(N), ep.out, ldc);
             LCE_COUNT_LAUNCH();
-            if (cuda_failed(cudaGetLastError())) rc = LCE_ERR_CUDA;
+            if (cuda_failed(err)) rc = LCE_ERR_CUDA;
         }
     }
     return rc;

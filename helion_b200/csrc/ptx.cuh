@@ -22,6 +22,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch. A kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream still runs; grid_dep_wait() returns once the predecessor has
+// finished and its writes are visible, so everything before it (barrier set-up, tensor-memory allocation)
+// overlaps the predecessor's tail. grid_dep_launch() lets the successor start early in the same way. Both are
+// no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -25,11 +25,13 @@ constexpr int kMergeLanes = 32;
 // written directly (lse[N], loss_rows[N]; 0 for ignored rows) and the statistics never reach memory.
 template <bool FINALIZE>
 __global__ void __launch_bounds__(kMergeRows * kMergeLanes)
-merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N,
+merge_partials_kernel(const float* partial, int n_tiles, long long row_stride, int N,
                       float* __restrict__ stats, const void* tgt, int tgt_i64, long long ignore_index,
                       float* __restrict__ lse, float* __restrict__ loss_rows) {
     __shared__ float sm[kMergeLanes][kMergeRows + 1], ss[kMergeLanes][kMergeRows + 1],
         st[kMergeLanes][kMergeRows + 1];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // `partial` is the preceding GEMM's output (this kernel may have started under its tail)
     const int r = threadIdx.x % kMergeRows;
     const int j = threadIdx.x / kMergeRows;
     const int row = blockIdx.x * kMergeRows + r;
@@ -70,10 +72,12 @@ merge_partials_kernel(const float* __restrict__ partial, int n_tiles, long long 
 __device__ __forceinline__ float block_sum_1024(float v, float* sh);
 
 __global__ void __launch_bounds__(1024)
-merge_finalize_small_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N,
+merge_finalize_small_kernel(const float* partial, int n_tiles, long long row_stride, int N,
                             const void* tgt, int tgt_i64, long long ignore_index, int reduction,
                             float* __restrict__ lse, float* __restrict__ loss, float* __restrict__ valid_count) {
     __shared__ float sh[1024], sm[1024], ss[1024], st[1024];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // `partial` is the preceding GEMM's output
     const int R = (N + 31) / 32 * 32;
     const int J = min(32, 1024 / R);
     const int r = threadIdx.x % R, j = threadIdx.x / R;
@@ -121,10 +125,12 @@ __device__ __forceinline__ void merge_top1(float& m, float& s, int& a, float bm,
 }
 
 __global__ void __launch_bounds__(kMergeRows * kMergeLanes)
-merge_top1_kernel(const float* __restrict__ partial, int n_tiles, long long row_stride, int N, long long vocab_start,
+merge_top1_kernel(const float* partial, int n_tiles, long long row_stride, int N, long long vocab_start,
                   long long* __restrict__ token, float* __restrict__ logprob, float* __restrict__ lse) {
     __shared__ float sm[kMergeLanes][kMergeRows + 1], ss[kMergeLanes][kMergeRows + 1];
     __shared__ int sa[kMergeLanes][kMergeRows + 1];
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // `partial` is the preceding GEMM's output
     const int r = threadIdx.x % kMergeRows, j = threadIdx.x / kMergeRows;
     const int row = blockIdx.x * kMergeRows + r;
     float m = -INFINITY, s = 0.f;
@@ -255,9 +261,11 @@ rowscale_kernel(const void* tgt, int tgt_i64, int N, long long ignore_index,
 // and writes the [rows, cols] result row-major. One thread per (tile, column quad, row): reads are
 // 16-byte coalesced along the rows of a tile.
 template <class T>
-__global__ void splitk_reduce_kernel(const float* __restrict__ scratch, int slices, long long slab_floats,
+__global__ void splitk_reduce_kernel(const float* scratch, int slices, long long slab_floats,
                                      int m_tiles, int n_tiles, int bn, int rows, int cols,
                                      T* __restrict__ out, long long ldo) {
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // `scratch` holds the slices of the preceding GEMM
     const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
     for (long long q = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; q < quads;
          q += static_cast<long long>(gridDim.x) * blockDim.x) {

@@ -68,13 +68,15 @@ __device__ __forceinline__ int topk_pow2_at_least(int n) {
 // than K columns). lse_out: [N] logsumexp of the scaled logits of this shard.
 template <class T>
 __global__ void __launch_bounds__(kTopkThreads)
-merge_topk_kernel(const float* __restrict__ partial, int n_tiles, int bn, long long row_stride, int N,
+merge_topk_kernel(const float* partial, int n_tiles, int bn, long long row_stride, int N,
                   const T* __restrict__ x, const T* __restrict__ w, int H, int V, float scale, long long vocab_start,
                   int K, float* __restrict__ top_val, long long* __restrict__ top_idx, float* __restrict__ lse_out) {
     __shared__ unsigned long long keys[kTopkSortN];
     __shared__ float red_m[kTopkThreads / 32], red_s[kTopkThreads / 32];
     const int row = blockIdx.x;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // `partial` is the preceding GEMM's output
     const float* rec = partial + row;
 
     // ---- logsumexp of the row: thread t folds tiles t, t + 256, ..., then lanes and warps in a fixed order

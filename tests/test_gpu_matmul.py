@@ -104,3 +104,26 @@ def test_larger_shapes_all_operand_layouts(dtype, m, n, k):
             out = helion_b200.matmul(av, bv)
             assert out.dtype == dtype and scaled_max_err(out, ref) <= 8e-3
     assert torch.equal(helion_b200.matmul(a, b), helion_b200.matmul(a, b))  # fixed summation order
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize(("m", "n", "k", "ldc"), [(70, 100, 64, 104), (300, 189, 128, 192), (129, 64, 72, 64), (31, 7, 64, 8)])
+def test_output_pitch_wider_than_the_row_through_the_c_abi(dtype, m, n, k, ldc):
+    """The C ABI takes the output pitch separately: rows of n values, ldc apart, n not a multiple of the 8 values
+    a 16-byte store holds. The line-wide epilogue stores must write n values per row and leave the gap alone."""
+    from helion_b200 import _lib
+
+    L = _lib.lib()
+    code = _lib.DTYPE_BF16 if dtype == torch.bfloat16 else _lib.DTYPE_F16
+    g = torch.Generator().manual_seed(m * n + k)
+    a = torch.randn(m, k, generator=g).to(dtype).to(DEV)
+    b = torch.randn(n, k, generator=g).to(dtype).to(DEV)  # given as [n][k]: b_mn_major = 0
+    c = torch.full((m, ldc), 7.0, dtype=dtype, device=DEV)
+    ws_bytes = L.lce_matmul_workspace_bytes(m, n, k, code, 0)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=DEV)
+    _lib.check(L.lce_matmul(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, 0, k, 0, k, ldc, code, ws.data_ptr(),
+                            ws_bytes, 0, torch.cuda.current_stream().cuda_stream), "lce_matmul")
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float().T
+    assert scaled_max_err(c[:, :n], ref) <= 8e-3
+    assert torch.all(c[:, n:] == 7.0), "values beyond the row's end were overwritten"
