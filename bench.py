@@ -281,7 +281,7 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         loss = step(x, t)
     barrier()
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, args.clock_period_ms / 1e3)
     sampler.start()  # every rank samples its own GPU; started here so that NVML's start-up is over by the timed region
     preheat_steps = 0
     t_heat = time.perf_counter()
@@ -410,7 +410,7 @@ def run_ours(args) -> None:
     # (best of ten 0.7 ms GEMMs on an idle GPU); K launches back to back each time, average duration.
     ms_fwd_hot = time_fwd_kernel()
     barrier()
-    rest_sampler = ClockSampler(local)
+    rest_sampler = ClockSampler(local, args.clock_period_ms / 1e3)
     rest_sampler.start()
     time.sleep(args.rest_s)
     rest_sampler.mark()
@@ -487,6 +487,8 @@ def main() -> None:
     ap.add_argument("--workload", default="llama3-8b",
                     help="llama3-8b (headline), gpt2-small, large-vocab, 14b-class, sweep-<rows>")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--clock-period-ms", type=float, default=5.0,
+                    help="period of the NVML clock / power samples taken during the timed regions")
     ap.add_argument("--rest-s", type=float, default=2.0,
                     help="idle seconds before the forward kernel is timed alone against the burst peak")
     ap.add_argument("--preheat-s", type=float, default=2.0,

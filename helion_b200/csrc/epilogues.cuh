@@ -114,6 +114,9 @@ __device__ __forceinline__ void store_block64(float* stage, int lane, int half, 
 // (tritium/ops/cross_entropy.py:235-248).
 // ---------------------------------------------------------------------------------------------
 struct EpiStats {
+    // The CTA that finishes last can merge the partial statistics and write logsumexp and loss itself
+    // (finish(), small batches of an unsharded vocabulary only): the forward is then ONE launch.
+    static constexpr bool kHasFinish = true;
     struct Params {
         const void* tgt;
         int tgt_i64;
@@ -122,7 +125,15 @@ struct EpiStats {
         long long vocab_start;  // global index of local column 0
         float* partial;
         long long row_stride;
+        // finish(): outputs of the fused tail (used only when the launch is given a completion counter)
+        float* fin_lse = nullptr;          // [rows]
+        float* fin_loss = nullptr;         // () for mean / sum, [rows] for none
+        float* fin_valid_count = nullptr;  // optional
+        int fin_reduction = 1;
+        long long fin_ignore_index = -100;
+        int fin_n_tiles = 0;
     };
+    static __device__ void finish(const Params& p);
     struct State {
         float m, s, t;
         int tcol;  // target column relative to the tile, or -1
@@ -185,6 +196,7 @@ struct EpiStats {
 // materialises the logits through matmul (examples/common.py:127-131, 380-384).
 // ---------------------------------------------------------------------------------------------
 struct EpiTop1 {
+    static constexpr bool kHasFinish = false;
     struct Params {
         int rows;   // valid rows
         int vocab;  // valid columns (local shard width)
@@ -253,6 +265,7 @@ constexpr int kTileTop = 8;
 constexpr int kTopRecord = 2 + 2 * kTileTop;
 
 struct EpiTopK {
+    static constexpr bool kHasFinish = false;
     struct Params {
         int rows;   // valid rows
         int vocab;  // valid columns (local shard width)
@@ -337,6 +350,7 @@ struct EpiTopK {
 // ---------------------------------------------------------------------------------------------
 template <class T>
 struct EpiGrad {
+    static constexpr bool kHasFinish = false;
     struct Params {
         const void* tgt;
         int tgt_i64;
@@ -439,6 +453,7 @@ enum StoreMode { kStoreDirect = 0, kStoreFirst = 1, kStoreAccum = 2, kStoreLast 
 
 template <class T>
 struct EpiStore {
+    static constexpr bool kHasFinish = false;
     struct Params {
         T* out;
         long long ldo;

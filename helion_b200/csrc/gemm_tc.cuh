@@ -118,7 +118,8 @@ template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                int m_tiles, int n_tiles, int k_blocks, int k_splits, int raster, int l2_hints,
-               const typename Epi::Params ep, int* __restrict__ status, int* __restrict__ sched_counter) {
+               const typename Epi::Params ep, int* __restrict__ status, int* __restrict__ sched_counter,
+               unsigned* __restrict__ done_counter) {
     using S = GemmSmem<BN, STAGES, CG>;
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(BN % (64 * CG) == 0 && BN >= 64 && BN <= 256, "tile width");
@@ -443,6 +444,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ptx::tc_fence_after_sync();
         if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
         else ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+    // Fused tail (epilogues that have one, launches that were given a completion counter): every CTA counts
+    // itself out once its outputs are visible device-wide; the one that counts last runs Epi::finish(). The
+    // counter wraps to zero with the last arrival, so it needs no reset between launches.
+    if constexpr (Epi::kHasFinish) {
+        if (done_counter != nullptr) {
+            __shared__ int counted_last;
+            __threadfence();  // this thread's epilogue stores, before the CTA is counted out
+            __syncthreads();
+            if (threadIdx.x == 0) counted_last = atomicInc(done_counter, gridDim.x - 1) == gridDim.x - 1;
+            __syncthreads();
+            if (counted_last) {
+                __threadfence();
+                Epi::finish(ep);
+            }
+        }
     }
 }
 

@@ -22,6 +22,11 @@
 namespace lce {
 
 __device__ int g_device_status = 0;
+// Completion counters of launches whose last CTA runs a fused tail (gemm_tc_kernel, done_counter). A launch takes
+// the next slot in turn; the counter returns to zero with the launch's last CTA, so a slot is ready for re-use
+// long before the turn comes round to it again (kDoneSlots launches later).
+constexpr int kDoneSlots = 4096;
+__device__ unsigned g_done_counters[kDoneSlots];
 
 namespace {
 
@@ -37,6 +42,8 @@ struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
     int* status_ptr = nullptr;
+    unsigned* done_counters = nullptr;  // kDoneSlots of them, zero when idle
+    mutable std::atomic<unsigned> next_done_slot{0};
 };
 
 DeviceInfo g_dev[kMaxDevices];
@@ -69,6 +76,8 @@ int device_info(DeviceInfo** out) {
             void* p = nullptr;
             if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return LCE_ERR_CUDA;
             d.status_ptr = static_cast<int*>(p);
+            if (cudaGetSymbolAddress(&p, g_done_counters) != cudaSuccess) return LCE_ERR_CUDA;
+            d.done_counters = static_cast<unsigned*>(p);
         }
         d.ready = true;
     }
@@ -209,7 +218,8 @@ cudaError_t launch_dependent(void (*kern)(KArgs...), int grid, int block, cudaSt
 
 template <int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
-                 int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream, int* sched) {
+                 int m_fastest, int k_splits, const typename Epi::Params& ep, cudaStream_t stream, int* sched,
+                 unsigned* done) {
     // Band the tile order so that the panels which co-running CTAs do NOT share stay resident in L2:
     // about 32 MB of them (the two L2 partitions of 63 MB each also hold the streaming operand).
     const long long kBandBytes = static_cast<long long>(g_tuning.band_mb.load(std::memory_order_relaxed)) << 20;
@@ -285,7 +295,7 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     if (counter != nullptr && cuda_failed(cudaMemsetAsync(counter, 0, sizeof(int), stream))) return LCE_ERR_CUDA;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
-                                               raster, l2_hints, ep, d.status_ptr, counter);
+                                               raster, l2_hints, ep, d.status_ptr, counter, done);
     LCE_COUNT_LAUNCH();
     return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
@@ -310,10 +320,10 @@ struct Path {
 template <bool A_MN, bool B_MN, bool IS_BF16, class Epi>
 int launch_tc(const DeviceInfo& d, int cg, const Mat& a, const Mat& b, long long M, long long Nn, long long K,
               int m_fastest, const typename Epi::Params& ep, cudaStream_t stream, int k_splits = 1,
-              int* sched = nullptr) {
+              int* sched = nullptr, unsigned* done = nullptr) {
     if (use_pair(M, cg))
-        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched);
-    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched);
+        return launch_tc_cg<2, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched, done);
+    return launch_tc_cg<1, A_MN, B_MN, IS_BF16, Epi>(d, a, b, M, Nn, K, m_fastest, k_splits, ep, stream, sched, done);
 }
 
 // The same for the CUDA-core GEMM (128 x 128 tiles, two CTAs per SM worth of work items).
@@ -420,6 +430,12 @@ FwdLayout fwd_layout(long long N, long long V, bool use_tc) {
     return l;
 }
 
+// HELION_B200_FUSED_TAIL=0 (tuning knob) keeps the forward tail of very small problems in its own launch.
+inline bool fused_tail_enabled() {
+    static const bool kEnabled = [] { const char* e = getenv("HELION_B200_FUSED_TAIL"); return e ? atoi(e) != 0 : true; }();
+    return kEnabled;
+}
+
 // What follows the logits GEMM: either the merged statistics of this shard (for a cross-shard merge)
 // or, when the shard is the whole vocabulary, logsumexp and per-row loss straight away.
 struct FwdOutputs {
@@ -451,10 +467,22 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
     ep.row_stride = l.row_stride;
     const Mat a{x, N, H, H}, b{w, V, H, H};
     int rc;
+    // Very small problems: the GEMM launch's last CTA does the tail itself (EpiStats::finish) - one launch in all.
+    // Its 192 threads fold a row's tiles one after the other, so this is only for few rows x few tiles.
+    unsigned* done = nullptr;
+    if (out.one_launch_tail && use_tc && fused_tail_enabled() && N * l.n_tiles <= 4096) {
+        ep.fin_lse = out.lse;
+        ep.fin_loss = out.loss;
+        ep.fin_valid_count = out.valid_count;
+        ep.fin_reduction = out.reduction;
+        ep.fin_ignore_index = out.ignore_index;
+        ep.fin_n_tiles = static_cast<int>(l.n_tiles);
+        done = d.done_counters + d.next_done_slot.fetch_add(1, std::memory_order_relaxed) % kDoneSlots;
+    }
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
             constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-            rc = launch_tc<false, false, kBf16, EpiStats>(d, cg, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream, 1, path.sched);
+            rc = launch_tc<false, false, kBf16, EpiStats>(d, cg, a, b, N, V, H, /*rows first: bands of X stay in L2, W streams*/ 1, ep, stream, 1, path.sched, done);
         } else {
             rc = LCE_ERR_ARG;
         }
@@ -462,6 +490,7 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
         rc = launch_simt<T, EpiStats>(d, a, false, b, false, N, V, H, ep, stream);
     }
     if (rc) return rc;
+    if (done != nullptr) return LCE_OK;
     const int blocks = static_cast<int>(cdiv(N, kMergeRows)), threads = kMergeRows * kMergeLanes;
     cudaError_t err;
     if (out.one_launch_tail)

@@ -116,6 +116,53 @@ merge_finalize_small_kernel(const float* partial, int n_tiles, long long row_str
     }
 }
 
+// The same tail inside the forward GEMM launch: run by all kGemmThreads threads of the CTA that finished last,
+// after every CTA's partial statistics are visible. Thread t takes rows t, t + kGemmThreads, ... and folds a
+// row's tiles in ascending order; the rows are then added lane by lane, warp by warp - fixed orders, so the
+// bits are the same on every run (they are not the bits of the separate-launch tails, whose orders differ).
+// The partials were written by other SMs during this launch: they are read past L1 (__ldcg).
+__device__ inline void EpiStats::finish(const Params& p) {
+    __shared__ float red_a[kGemmThreads / 32], red_b[kGemmThreads / 32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    float nll = 0.f, cnt = 0.f;
+    for (int r = t; r < p.rows; r += kGemmThreads) {
+        float m = -INFINITY, s = 0.f, tl = -INFINITY;
+        for (int b = 0; b < p.fin_n_tiles; ++b) {
+            const float* base = p.partial + static_cast<long long>(b) * 3 * p.row_stride + r;
+            merge_ms(m, s, __ldcg(base), __ldcg(base + p.row_stride));
+            tl = fmaxf(tl, __ldcg(base + 2 * p.row_stride));
+        }
+        const float l = m + logf(s);
+        p.fin_lse[r] = l;
+        const bool valid = load_target(p.tgt, p.tgt_i64, r) != p.fin_ignore_index;
+        const float row_nll = valid ? (l - tl) : 0.f;
+        if (p.fin_reduction == 0) p.fin_loss[r] = row_nll;  // LCE_REDUCTION_NONE
+        nll += row_nll;
+        cnt += valid ? 1.f : 0.f;
+    }
+    if (p.fin_reduction == 0 && p.fin_valid_count == nullptr) return;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        nll += __shfl_xor_sync(0xffffffffu, nll, off);
+        cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+    }
+    if (lane == 0) {
+        red_a[warp] = nll;
+        red_b[warp] = cnt;
+    }
+    __syncthreads();
+    if (t == 0) {
+        float total = 0.f, count = 0.f;
+        for (int k = 0; k < kGemmThreads / 32; ++k) {
+            total += red_a[k];
+            count += red_b[k];
+        }
+        if (p.fin_reduction == 1) *p.fin_loss = total / count;  // mean; count == 0 -> NaN, as torch
+        else if (p.fin_reduction == 2) *p.fin_loss = total;
+        if (p.fin_valid_count) *p.fin_valid_count = count;
+    }
+}
+
 // Greedy head: partial [n_tiles][3][row_stride] of EpiTop1 -> token[N] (global vocabulary index of the
 // largest logit; the lowest index on ties), logprob[N] = log softmax at that token, optionally lse[N].
 // Same CTA shape and fold order as merge_partials_kernel.
@@ -230,6 +277,7 @@ rowscale_kernel(const void* tgt, int tgt_i64, int N, long long ignore_index,
                 const float* __restrict__ valid_count, float* __restrict__ rowscale) {
     __shared__ int warp_counts[8];
     __shared__ float count_sh;
+    ptx::grid_dep_launch();  // the GEMM that follows may set itself up now; it waits for this grid before it reads
     float count = 1.f;
     if (mean) {
         if (valid_count != nullptr) {
