@@ -17,10 +17,12 @@ def bench_repeats() -> int:
 def do_bench(fn, warmup_ms: float = 25.0, rep_ms: float = 100.0) -> float:
     """Mean device time of ``fn`` in ms. Like ``triton.testing.do_bench``: the run count comes from a
     time budget, and a 256 MB buffer is overwritten before every timed run so each run starts with a
-    cold L2."""
+    cold L2 (``HELION_BENCH_FLUSH=0`` shrinks that write to 4 bytes: same launches, L2 left as the previous
+    run left it)."""
     fn()
     torch.cuda.synchronize()
-    cache = torch.empty(256 << 20, dtype=torch.int8, device="cuda")
+    flush = os.environ.get("HELION_BENCH_FLUSH", "1") != "0"
+    cache = torch.empty((256 << 20) if flush else 4, dtype=torch.int8, device="cuda")
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(5):

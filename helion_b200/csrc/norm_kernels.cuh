@@ -246,6 +246,59 @@ rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
 }
 
 // ---------------------------------------------------------------------------------------------
+// Plain forward, one row per CTA: what measured fastest for the plain (non-residual) forward of rows of
+// 2 KB and more. HBM bandwidth needs bytes in flight, and here they come from MANY small CTAs per SM rather
+// than from a few large ones: a CTA of 128 (or 256) threads holds its row in VPT 16-byte vectors per thread,
+// keeps nothing else across the row sum - the weights are fetched after it, out of L1/L2 - and so stays at
+// 40-85 registers (1536 / 1152 / 768 resident threads per SM for 2 / 4 / 8 vectors per thread: 50-100 KB of
+// loads in flight per SM); the grid is one CTA per row and the hardware deals them out as CTAs retire.
+// ---------------------------------------------------------------------------------------------
+template <class T, int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS, (VPT <= 2 ? 1536 : (VPT == 4 ? 1152 : 768)) / THREADS)
+rms_forward_row_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ out,
+                       float* __restrict__ rstd_out, int n_rows, int H, float eps) {
+    constexpr int VEC = RmsTile<T>::kVec;
+    __shared__ float red[THREADS / 32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const float inv_h = 1.0f / static_cast<float>(H);
+    for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        const T* xr = x + static_cast<long long>(row) * H;
+        T* orow = out + static_cast<long long>(row) * H;
+        uint4 rx[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) rx[i] = rms_load<T, true>(xr, (i * THREADS + t) * VEC, H);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float z[VEC];
+            rms_unpack<T>(rx[i], z);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) ss = fmaf(z[j], z[j], ss);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();  // `red` of the previous row has been read by everyone
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int k = 0; k < THREADS / 32; ++k) total += red[k];  // same order in every thread
+        const float rstd = rms_rstd(total, inv_h, eps);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = (i * THREADS + t) * VEC;
+            float z[VEC], w[VEC];
+            rms_unpack<T>(rx[i], z);
+            rms_unpack<T>(rms_load<T, true>(weight, c, H), w);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) z[j] = z[j] * rstd * w[j];
+            rms_store<T, true>(orow, c, H, rms_pack<T>(z));
+        }
+        if (t == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Ring kernels: the form every 16-byte-aligned problem takes.
 //
 // A row is only a few KB, so what keeps HBM busy is how many bytes a CTA has in flight - and registers

@@ -538,3 +538,34 @@ def test_fused_dx_reduce_scatter_emulated_on_one_gpu(world):
     assert all(torch.equal(f, dx) for f in finals)
     assert scaled_max_err(torch.cat(dws), wr.grad.float()) <= 8e-3
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(16, 512, 1024), (128, 512, 1024), (128, 1024, 8192), (100, 264, 777), (1, 64, 300)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_very_small_problems_run_the_forward_in_one_launch(shape, reduction):
+    """Few rows x few vocabulary tiles: the GEMM launch's last CTA merges the statistics and writes logsumexp and
+    loss itself. One launch per forward, the oracle's loss, and the same bits call after call - more calls
+    than the library has completion counters, so every counter is used again."""
+    n, h, v = shape
+    g = torch.Generator().manual_seed(n + h + v)
+    x = torch.randn(n, h, generator=g).to(torch.float16).to(DEV)
+    w = (torch.randn(v, h, generator=g) / h ** 0.5).to(torch.float16).to(DEV)
+    t = torch.randint(0, v, (n,), generator=g)
+    if n > 4:
+        t[::5] = -100
+    t = t.to(DEV)
+    L = _lib.lib()
+    first = ops.linear_cross_entropy(x, w, t, reduction=reduction)
+    torch.cuda.synchronize()
+    before = L.lce_launch_count()
+    again = ops.linear_cross_entropy(x, w, t, reduction=reduction)
+    torch.cuda.synchronize()
+    assert L.lce_launch_count() - before == 1
+    assert torch.equal(first, again)
+    ref = F.cross_entropy(F.linear(x.float(), w.float()), t, reduction=reduction)
+    torch.testing.assert_close(first.float(), ref, rtol=2e-3, atol=2e-3)
+    if reduction == "mean" and shape == (16, 512, 1024):
+        for _ in range(4200):
+            again = ops.linear_cross_entropy(x, w, t, reduction=reduction)
+        assert torch.equal(first, again)
+        assert _lib.device_status() == 0
