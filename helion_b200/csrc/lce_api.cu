@@ -1816,21 +1816,20 @@ int rms_forward_launch(const DeviceInfo& d, const RmsShape& sh, const void* x, c
     T* rop = static_cast<T*>(residual_out);
     const int n = static_cast<int>(n_rows), h = static_cast<int>(H);
     if constexpr (!RESIDUAL) {
-        // Plain forward of 16-byte-aligned rows of 2 KB and more: one small CTA per row (rms_forward_row_kernel).
-        // HELION_B200_RMS_ROW=0 (tuning knob) falls back to the ring / register kernels below.
+        // Plain forward of 16-byte-aligned rows of 8 KB and more: one small CTA per row (rms_forward_row_kernel);
+        // narrower rows measured faster on the register kernels below, which pack several rows into a CTA.
+        // HELION_B200_RMS_ROW=0 (tuning knob) falls back to the ring / register kernels for every width.
         static const int kRowKernel = [] { const char* e = getenv("HELION_B200_RMS_ROW"); return e ? atoi(e) : 1; }();
         constexpr long long kVec = 16 / sizeof(T);
         const long long nvec = H / kVec;
-        if (kRowKernel != 0 && sh.vector && !sh.wide && H * static_cast<long long>(sizeof(T)) >= 2048 && nvec <= 256 * 8) {
+        if (kRowKernel != 0 && sh.vector && !sh.wide && H * static_cast<long long>(sizeof(T)) >= 8192 && nvec <= 256 * 8) {
             const int threads = nvec <= 128 * 4 ? 128 : 256;
             const long long per_thread = cdiv(nvec, threads);
             const int grid = static_cast<int>(n_rows);
 #define LCE_RMS_ROW(VPT, THREADS) \
     rms_forward_row_kernel<T, VPT, THREADS><<<grid, THREADS, 0, s>>>(xp, wp, op, rstd, n, h, eps)
-            if (threads == 128) {
-                if (per_thread <= 1) LCE_RMS_ROW(1, 128);
-                else if (per_thread <= 2) LCE_RMS_ROW(2, 128);
-                else LCE_RMS_ROW(4, 128);
+            if (threads == 128) {  // 8 KB rows: exactly four vectors per thread
+                LCE_RMS_ROW(4, 128);
             } else {
                 if (per_thread <= 4) LCE_RMS_ROW(4, 256);
                 else LCE_RMS_ROW(8, 256);

@@ -247,7 +247,7 @@ rms_forward_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
 
 // ---------------------------------------------------------------------------------------------
 // Plain forward, one row per CTA: what measured fastest for the plain (non-residual) forward of rows of
-// 2 KB and more. HBM bandwidth needs bytes in flight, and here they come from MANY small CTAs per SM rather
+// 8 KB and more. HBM bandwidth needs bytes in flight, and here they come from MANY small CTAs per SM rather
 // than from a few large ones: a CTA of 128 (or 256) threads holds its row in VPT 16-byte vectors per thread,
 // keeps nothing else across the row sum - the weights are fetched after it, out of L1/L2 - and so stays at
 // 40-85 registers (1536 / 1152 / 768 resident threads per SM for 2 / 4 / 8 vectors per thread: 50-100 KB of
