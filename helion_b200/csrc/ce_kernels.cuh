@@ -186,7 +186,7 @@ __device__ __forceinline__ int ce_target_slot(long long col0, long long target) 
 // FINAL (n_groups == 1): writes lse / loss_rows; else partial statistics
 // partial[(group*3 + c) * row_stride + row].
 template <class T, bool VECTOR, bool FINAL>
-__global__ void __launch_bounds__(kCeThreads, 3)
+__global__ void __launch_bounds__(kCeThreads, 4)  // 64 registers: 1024 threads x 64 B of loads in flight per SM
 ce_row_stats_kernel(const T* __restrict__ logits, const void* tgt, int tgt_i64, int N, long long V, int n_chunks,
                     int n_groups, float* __restrict__ partial, long long row_stride, long long ignore_index,
                     float* __restrict__ lse, float* __restrict__ loss_rows) {
