@@ -50,16 +50,22 @@ def test_gemm_wait_runs_out_with_a_status_code_and_the_next_launch_is_fine(short
 
 
 def test_rmsnorm_ring_wait_runs_out_with_code_111(short_waits):
-    # 2048 rows of 8 KB: the plain forward streams these through the shared-memory ring
-    x = torch.randn(2048, 4096, device=DEV).bfloat16()
-    w = torch.randn(4096, device=DEV).bfloat16()
-    norm_ops.rmsnorm(x, w)
+    # the RMSNorm backward streams its rows through the shared-memory ring (the plain forward of rows this wide
+    # runs on the one-row-per-CTA kernel, which has no waits)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2048, 4096, generator=g).bfloat16().to(DEV)
+    dy = torch.randn(2048, 4096, generator=g).bfloat16().to(DEV)
+    w = torch.randn(4096, generator=g).bfloat16().to(DEV)
+    norm_ops.rmsnorm_backward(dy, x, w)
     torch.cuda.synchronize()
     assert _lib.device_status() == 111
     assert _lib.device_status() == 0
     _lib.check(_lib.lib().lce_debug_wait_test(0, 0), "lce_debug_wait_test")
-    out = norm_ops.rmsnorm(x, w)
+    dx, dweight = norm_ops.rmsnorm_backward(dy, x, w)
     torch.cuda.synchronize()
-    ref = x.float() * torch.rsqrt(x.float().pow(2).mean(dim=-1, keepdim=True) + 1e-6) * w.float()
-    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    xr = x.float().requires_grad_(True)
+    wr = w.float().requires_grad_(True)
+    (xr * torch.rsqrt(xr.pow(2).mean(dim=-1, keepdim=True) + 1e-6) * wr).backward(dy.float())
+    torch.testing.assert_close(dx.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dweight.float(), wr.grad, rtol=2e-2, atol=0.5)
     assert _lib.device_status() == 0
