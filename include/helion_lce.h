@@ -11,9 +11,12 @@
  *   - every pointer is a device pointer owned by the caller unless stated otherwise; the library
  *     allocates nothing at call time and keeps no reference after the call returns. The one piece of
  *     device memory it owns is compiled into its image: the 16 MiB scratch array of
- *     lce_forward_stats_static (plus a 4-byte status word), held by every GPU that loads the library;
+ *     lce_forward_stats_static (plus a 4-byte status word and 16 KB of completion counters used by
+ *     one-launch forwards of very small problems), held by every GPU that loads the library;
  *   - a call only enqueues work on `stream` (a cudaStream_t passed as void*) of the current
- *     device and returns; it never synchronises;
+ *     device and returns; it never synchronises. Kernels of one call may be launched with programmatic
+ *     stream serialization (they wait on the device for their predecessor before they read its results);
+ *     towards the work before and after the call the stream order is the ordinary one;
  *   - return value 0 = enqueued; anything else is a synchronous argument / launch error, see
  *     lce_strerror(). There is no CPU fallback: a device that is not sm_100 yields LCE_ERR_ARCH;
  *   - x is [N, H] row-major, w is [V_local, H] row-major (rows vocab_start .. vocab_start+V_local
