@@ -470,7 +470,11 @@ int forward_stats_impl(const DeviceInfo& d, const Path& path, const void* x, con
     // Very small problems: the GEMM launch's last CTA does the tail itself (EpiStats::finish) - one launch in all.
     // Its 192 threads fold a row's tiles one after the other, so this is only for few rows x few tiles.
     unsigned* done = nullptr;
-    if (out.one_launch_tail && use_tc && fused_tail_enabled() && N * l.n_tiles <= 4096) {
+    // Not while the stream is being captured: a graph would carry its counter into every replay, where it could
+    // meet a later launch that was dealt the same one.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (out.one_launch_tail && use_tc && fused_tail_enabled() && N * l.n_tiles <= 4096 &&
+        cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone) {
         ep.fin_lse = out.lse;
         ep.fin_loss = out.loss;
         ep.fin_valid_count = out.valid_count;
