@@ -114,19 +114,38 @@ __device__ __forceinline__ void tile_coords(int tile, int m_units, int n_tiles, 
 // k blocks [slice * per, (slice+1) * per) and hands the epilogue a partial sum tagged with its slice
 // (the epilogue stores slices side by side; a later pass adds them in slice order). The host
 // guarantees that every slice is non-empty.
-template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi>
+// An optional SECOND product computed by the same launch (same tile shape, B layout, element type and epilogue
+// kind; its own operands, sizes, A layout and epilogue parameters). Its work items follow the first product's in
+// the round-robin deal, so two small independent products - the backward's dX and dW for a handful of tokens -
+// share one launch instead of running one after the other. Static deal only.
+struct NoSecondGemm {
+    static constexpr bool kPresent = false;
+    static constexpr bool kAMn = false;
+};
+template <class Epi, bool A_MN2>
+struct SecondGemm {
+    static constexpr bool kPresent = true;
+    static constexpr bool kAMn = A_MN2;
+    CUtensorMap tmA, tmB;
+    int m_tiles, n_tiles, k_blocks, k_splits, raster;
+    typename Epi::Params ep;
+};
+
+template <int BN, int STAGES, int CG, bool A_MN, bool B_MN, bool IS_BF16, class Epi, class Second = NoSecondGemm>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                int m_tiles, int n_tiles, int k_blocks, int k_splits, int raster, int l2_hints,
                const typename Epi::Params ep, int* __restrict__ status, int* __restrict__ sched_counter,
-               unsigned* __restrict__ done_counter) {
+               unsigned* __restrict__ done_counter, const __grid_constant__ Second second = Second{}) {
     using S = GemmSmem<BN, STAGES, CG>;
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(BN % (64 * CG) == 0 && BN >= 64 && BN <= 256, "tile width");
     static_assert(2 * BN <= 512, "two accumulator buffers must fit in tensor memory");
     constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
     constexpr uint32_t kIdesc = ptx::make_idesc_f16(kBM * CG, BN, IS_BF16, A_MN, B_MN);
+    constexpr uint32_t kIdesc2 = ptx::make_idesc_f16(kBM * CG, BN, IS_BF16, Second::kAMn, B_MN);
     constexpr bool kPair = CG == 2;
+    constexpr bool kDual = Second::kPresent;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -156,8 +175,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int unit_step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     const int m_units = kPair ? (m_tiles + 1) / 2 : m_tiles;
     const int total_units = m_units * n_tiles;
-    const int total_work = total_units * k_splits;
+    const int work_first = total_units * k_splits;  // work items of the first product
     const int kb_per_slice = (k_blocks + k_splits - 1) / k_splits;
+    int total_work = work_first;
+    if constexpr (kDual)
+        total_work += (kPair ? (second.m_tiles + 1) / 2 : second.m_tiles) * second.n_tiles * second.k_splits;
+    // Which product a work item belongs to, and that product's tiling.
+    struct Item {
+        bool sec;
+        int w, m_units, n_tiles, total_units, k_blocks, kb_per_slice, raster;
+    };
+    auto item_of = [&](int work) {
+        Item it{false, work, m_units, n_tiles, total_units, k_blocks, kb_per_slice, raster};
+        if constexpr (kDual) {
+            if (work >= work_first) {
+                it.sec = true;
+                it.w = work - work_first;
+                it.m_units = kPair ? (second.m_tiles + 1) / 2 : second.m_tiles;
+                it.n_tiles = second.n_tiles;
+                it.total_units = it.m_units * it.n_tiles;
+                it.k_blocks = second.k_blocks;
+                it.kb_per_slice = (second.k_blocks + second.k_splits - 1) / second.k_splits;
+                it.raster = second.raster;
+            }
+        }
+        return it;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -250,11 +293,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     drawn = nxt < total_work ? unit_step + atomicAdd(sched_counter, 1) : total_work;
                 }
                 int m_unit, n_tile;
-                tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
-                const int kb_begin = (work / total_units) * kb_per_slice;
-                const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
+                const Item it = item_of(work);
+                tile_coords(it.w % it.total_units, it.m_units, it.n_tiles, it.raster, m_unit, n_tile);
+                const int kb_begin = (it.w / it.total_units) * it.kb_per_slice;
+                const int kb_end = min(it.k_blocks, kb_begin + it.kb_per_slice);
                 const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
                 const int b_row0 = n_tile * BN + static_cast<int>(cta_rank) * S::kBRows;
+                const CUtensorMap* ta = &tmA;
+                const CUtensorMap* tb = &tmB;
+                bool a_mn = A_MN;
+                if constexpr (kDual) {
+                    if (it.sec) {
+                        ta = &second.tmA;
+                        tb = &second.tmB;
+                        a_mn = Second::kAMn;
+                    }
+                }
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const uint32_t stage = issued % STAGES;
                     const uint32_t phase = (issued / STAGES) & 1u;
@@ -267,26 +321,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // the barrier the MMA issuer waits on: our own, or the leader's for a pair
                     const uint32_t fb = kPair ? leader_full0 + 8u * stage : full_bar(stage);
                     auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
-                        const uint64_t policy = (tm == &tmA) ? policy_a : policy_b;
+                        const uint64_t policy = (tm == ta) ? policy_a : policy_b;
                         if constexpr (kPair) ptx::tma_load_2d_pair_hint(dst, tm, fb, x, y, policy);
                         else ptx::tma_load_2d_hint(dst, tm, fb, x, y, policy);
                     };
                     // bytes of the whole group's copies for this stage, announced by the leader only
                     if (cta_rank == 0)
                         ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes * CG + (issued == 0 ? announce_extra : 0u));
-                    if constexpr (!A_MN) {
-                        load(sa, &tmA, kb * kBK, m_tile * kBM);
+                    if (!a_mn) {  // a constant unless the launch carries a second product
+                        load(sa, ta, kb * kBK, m_tile * kBM);
                     } else {
 #pragma unroll
                         for (int j = 0; j < kBM / 64; ++j)
-                            load(sa + j * (kBK * 128), &tmA, m_tile * kBM + j * 64, kb * kBK);
+                            load(sa + j * (kBK * 128), ta, m_tile * kBM + j * 64, kb * kBK);
                     }
                     if constexpr (!B_MN) {
-                        load(sb, &tmB, kb * kBK, b_row0);
+                        load(sb, tb, kb * kBK, b_row0);
                     } else {
 #pragma unroll
                         for (int j = 0; j < S::kBRows / 64; ++j)
-                            load(sb + j * (kBK * 128), &tmB, b_row0 + j * 64, kb * kBK);
+                            load(sb + j * (kBK * 128), tb, b_row0 + j * 64, kb * kBK);
                     }
                     ++issued;
                 }
@@ -326,8 +380,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t local_tile = 0;
             bool ok = true;
             for (int work = unit0; work < total_work && ok; ++local_tile) {
-                const int kb_begin = (work / total_units) * kb_per_slice;
-                const int kb_end = min(k_blocks, kb_begin + kb_per_slice);
+                const Item it = item_of(work);
+                const int kb_begin = (it.w / it.total_units) * it.kb_per_slice;
+                const int kb_end = min(it.k_blocks, kb_begin + it.kb_per_slice);
+                const bool a_mn = it.sec ? Second::kAMn : A_MN;
+                const uint32_t idesc = it.sec ? kIdesc2 : kIdesc;
                 const uint32_t buf = local_tile & 1u;
                 const uint32_t buf_phase = (local_tile >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty_bar(buf), buf_phase ^ 1u, abort_flag)) {
@@ -351,14 +408,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         // K-major: 16 elements = 32 bytes further along the swizzled row.
                         // MN-major: 16 k-rows of 128 bytes further down.
                         const uint64_t da =
-                            A_MN ? ptx::make_smem_desc(sa + k * (kUmmaK * 128), kBK * 128, 1024)
+                            a_mn ? ptx::make_smem_desc(sa + k * (kUmmaK * 128), kBK * 128, 1024)
                                  : ptx::make_smem_desc(sa + k * (kUmmaK * 2), 0, 1024);
                         const uint64_t db =
                             B_MN ? ptx::make_smem_desc(sb + k * (kUmmaK * 128), kBK * 128, 1024)
                                  : ptx::make_smem_desc(sb + k * (kUmmaK * 2), 0, 1024);
                         const uint32_t acc = (kb != kb_begin || k != 0) ? 1u : 0u;  // first MMA of a tile overwrites
-                        if constexpr (kPair) ptx::umma_f16_pair(tmem_d, da, db, kIdesc, acc);
-                        else ptx::umma_f16(tmem_d, da, db, kIdesc, acc);
+                        if constexpr (kPair) ptx::umma_f16_pair(tmem_d, da, db, idesc, acc);
+                        else ptx::umma_f16(tmem_d, da, db, idesc, acc);
                     }
                     // smem slot reusable (in both CTAs of a pair) once these MMAs retire
                     if constexpr (kPair) ptx::umma_commit_pair(empty_bar(stage), 3);
@@ -388,13 +445,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         typename Epi::State st;
         for (int work = unit0; work < total_work && ok; ++local_tile) {
             int m_unit, n_tile;
-            tile_coords(work % total_units, m_units, n_tiles, raster, m_unit, n_tile);
+            const Item it = item_of(work);
+            tile_coords(it.w % it.total_units, it.m_units, it.n_tiles, it.raster, m_unit, n_tile);
             const int m_tile = kPair ? 2 * m_unit + static_cast<int>(cta_rank) : m_unit;
             const uint32_t buf = local_tile & 1u;
             const uint32_t buf_phase = (local_tile >> 1) & 1u;
-            TileCtx tc{m_tile, n_tile, n_tiles, quarter * 32 + lane, BN, work / total_units,
+            TileCtx tc{m_tile, n_tile, it.n_tiles, quarter * 32 + lane, BN, it.w / it.total_units,
                        reinterpret_cast<float*>(gen_bar_base + S::kBarrierBytes) + (warp - 2) * kStageFloatsPerWarp};
-            Epi::begin(st, ep, tc);  // global loads for this row overlap the wait below
+            const typename Epi::Params* epp = &ep;  // this product's epilogue parameters
+            if constexpr (kDual) {
+                if (it.sec) epp = &second.ep;
+            }
+            Epi::begin(st, *epp, tc);  // global loads for this row overlap the wait below
             if (!ptx::mbar_wait(tfull_bar(buf), buf_phase, abort_flag)) {
                 ok = false;
                 break;
@@ -409,10 +471,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int c = 0; c < BN / 32; c += 2) {
                 ptx::tmem_ld_wait();
                 ptx::tmem_ld_32x32(taddr + (c + 1) * 32, vb);
-                Epi::chunk(st, ep, tc, c * 32, va);
+                Epi::chunk(st, *epp, tc, c * 32, va);
                 ptx::tmem_ld_wait();
                 if (c + 2 < BN / 32) ptx::tmem_ld_32x32(taddr + (c + 2) * 32, va);
-                Epi::chunk(st, ep, tc, (c + 1) * 32, vb);
+                Epi::chunk(st, *epp, tc, (c + 1) * 32, vb);
             }
             // all TMEM reads of this buffer are done: hand it back to the MMA issuer
             ptx::tc_fence_before_sync();
@@ -421,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
                 else ptx::mbar_arrive(tempty_bar(buf));
             }
-            Epi::end(st, ep, tc);
+            Epi::end(st, *epp, tc);
             // every lane reads the next work item; one lane releases the ring slot for the warp
             const int following = next_work(work, local_tile, false, ok);
             if (dyn && ok) {

@@ -295,7 +295,65 @@ int launch_tc_cg(const DeviceInfo& d, const Mat& a, const Mat& b, long long M, l
     if (counter != nullptr && cuda_failed(cudaMemsetAsync(counter, 0, sizeof(int), stream))) return LCE_ERR_CUDA;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma, tmb, static_cast<int>(m_tiles),
                                                static_cast<int>(n_tiles), static_cast<int>(k_blocks), k_splits,
-                                               raster, l2_hints, ep, d.status_ptr, counter, done);
+                                               raster, l2_hints, ep, d.status_ptr, counter, done, NoSecondGemm{});
+    LCE_COUNT_LAUNCH();
+    return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
+}
+
+// Two independent products with the same epilogue kind in ONE launch of single-CTA tiles: the first with a
+// K-major A operand, the second with an MN-major one, both with MN-major B (the backward's dX = G W and
+// dW = G^T X). Work items of the second follow those of the first in the round-robin deal.
+struct GemmProblem {
+    Mat a, b;
+    long long M, Nn, K;
+    int k_splits;
+};
+template <bool IS_BF16, class Epi>
+int launch_tc_two(const DeviceInfo& d, const GemmProblem& p1, const typename Epi::Params& ep1, const GemmProblem& p2,
+                  const typename Epi::Params& ep2, cudaStream_t stream) {
+    constexpr int dtype = IS_BF16 ? LCE_DTYPE_BF16 : LCE_DTYPE_F16;
+    using Second = SecondGemm<Epi, true>;
+    CUtensorMap tma1, tmb1;
+    Second sec;
+    int rc;
+    if ((rc = make_tmap(&tma1, p1.a.ptr, dtype, p1.K, p1.M, p1.a.pitch_elems * 2, kBK, kBM))) return rc;      // K-major A
+    if ((rc = make_tmap(&tmb1, p1.b.ptr, dtype, p1.Nn, p1.K, p1.b.pitch_elems * 2, 64, kBK))) return rc;       // MN-major B
+    if ((rc = make_tmap(&sec.tmA, p2.a.ptr, dtype, p2.M, p2.K, p2.a.pitch_elems * 2, 64, kBK))) return rc;    // MN-major A
+    if ((rc = make_tmap(&sec.tmB, p2.b.ptr, dtype, p2.Nn, p2.K, p2.b.pitch_elems * 2, 64, kBK))) return rc;   // MN-major B
+    const long long mt1 = cdiv(p1.M, kBM), nt1 = cdiv(p1.Nn, kBN), kb1 = cdiv(p1.K, kBK);
+    const long long mt2 = cdiv(p2.M, kBM), nt2 = cdiv(p2.Nn, kBN), kb2 = cdiv(p2.K, kBK);
+    if (mt1 * nt1 * p1.k_splits + mt2 * nt2 * p2.k_splits > 0x3fffffffll) return LCE_ERR_TOO_LARGE;
+    if (mt1 * nt1 == 0 || mt2 * nt2 == 0 || kb1 == 0 || kb2 == 0) return LCE_ERR_ARG;
+    if (p1.k_splits < 1 || (p1.k_splits - 1) * cdiv(kb1, p1.k_splits) >= kb1) return LCE_ERR_ARG;
+    if (p2.k_splits < 1 || (p2.k_splits - 1) * cdiv(kb2, p2.k_splits) >= kb2) return LCE_ERR_ARG;
+    sec.m_tiles = static_cast<int>(mt2);
+    sec.n_tiles = static_cast<int>(nt2);
+    sec.k_blocks = static_cast<int>(kb2);
+    sec.k_splits = p2.k_splits;
+    sec.raster = -static_cast<int>(nt2);  // columns fastest: small problems, everything stays in L2
+    sec.ep = ep2;
+    auto kern = gemm_tc_kernel<kBN, kStages1, 1, false, true, IS_BF16, Epi, Second>;
+    constexpr int smem = GemmSmem<kBN, kStages1, 1>::kTotalBytes;
+    static std::atomic<bool> smem_opted_in[kMaxDevices];
+    if (!smem_opted_in[d.index].load(std::memory_order_acquire)) {
+        if (cuda_failed(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return LCE_ERR_CUDA;
+        smem_opted_in[d.index].store(true, std::memory_order_release);
+    }
+    const long long work = mt1 * nt1 * p1.k_splits + mt2 * nt2 * p2.k_splits;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(work < d.sm_count ? work : d.sm_count));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tma1, tmb1, static_cast<int>(mt1), static_cast<int>(nt1),
+                                               static_cast<int>(kb1), p1.k_splits, -static_cast<int>(nt1), 0, ep1,
+                                               d.status_ptr, static_cast<int*>(nullptr),
+                                               static_cast<unsigned*>(nullptr), sec);
     LCE_COUNT_LAUNCH();
     return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
 }
@@ -685,6 +743,12 @@ inline int wide_stores(const void* out, long long ld) {
     return (kEnabled != 0 && aligned16(out) && ld % 8 == 0) ? 1 : 0;
 }
 
+// HELION_B200_BWD_ONE=0 (tuning knob) keeps the dX and dW GEMMs of very small batches in separate launches.
+inline bool two_products_enabled() {
+    static const bool kEnabled = [] { const char* e = getenv("HELION_B200_BWD_ONE"); return e ? atoi(e) != 0 : true; }();
+    return kEnabled;
+}
+
 // Small batches skip the rowscale launch: the recompute epilogue derives the per-row factor itself.
 inline bool fold_rowscale(long long N) { return N <= 1024; }
 
@@ -746,6 +810,53 @@ int backward_impl(const DeviceInfo& d, const Path& path, const BwdPlan& p, const
                 if (rc) return rc;
             }
             const Mat gm{g, nr, nc, p.ldg};
+            // ---- steps 2 and 3 in one launch for a handful of tokens: dX and dW both read G and are independent
+            // of each other, and at this size each is a few tiles that a launch of its own would only wait for
+            bool both_done = false;
+            if constexpr (sizeof(T) == 2 && std::is_same<TDx, T>::value) {
+                if (use_tc && need_dx && need_dw && N <= 128 && p.n_rblk == 1 && p.n_cblk == 1 && scatter == nullptr &&
+                    dx_events == nullptr && dw_sumsq == nullptr && two_products_enabled()) {
+                    typename EpiStore<T>::Params e1, e2;
+                    e1.out = static_cast<T*>(dx);
+                    e1.ldo = H;
+                    e1.rows = static_cast<int>(nr);
+                    e1.cols = static_cast<int>(H);
+                    e1.scratch = reinterpret_cast<float*>(ws + p.off_dx_scratch);
+                    e1.mode = p.dx_splits > 1 ? kStoreSlice : kStoreDirect;
+                    e1.slab_floats = p.dx_slab_floats;
+                    e1.peer_world = 0;
+                    e1.wide = wide_stores(e1.out, H);
+                    e2.out = static_cast<T*>(dw);
+                    e2.ldo = H;
+                    e2.rows = static_cast<int>(nc);
+                    e2.cols = static_cast<int>(H);
+                    e2.scratch = reinterpret_cast<float*>(ws + p.off_dw_scratch);
+                    e2.mode = p.dw_splits > 1 ? kStoreSlice : kStoreDirect;
+                    e2.slab_floats = p.dw_band_scratch_floats;
+                    e2.peer_world = 0;
+                    e2.wide = wide_stores(e2.out, H);
+                    const GemmProblem q1{gm, Mat{wp, nc, H, H}, nr, H, nc, p.dx_splits};
+                    const GemmProblem q2{gm, Mat{xp, nr, H, H}, nc, H, nr, p.dw_splits};
+                    if ((rc = launch_tc_two<kBf16, EpiStore<T>>(d, q1, e1, q2, e2, stream))) return rc;
+                    const int bn = static_cast<int>(p.bn);
+                    const int n_tiles = static_cast<int>(cdiv(H, bn));
+                    auto sum_slices = [&](const typename EpiStore<T>::Params& e, int splits, long long rows) -> int {
+                        if (splits <= 1) return LCE_OK;
+                        const int m_tiles = static_cast<int>(cdiv(rows, kBM));
+                        const long long quads = static_cast<long long>(m_tiles) * n_tiles * (bn / 4) * kBM;
+                        const int blocks = static_cast<int>(cdiv(quads, 256) < 4096 ? cdiv(quads, 256) : 4096);
+                        const cudaError_t err = launch_dependent(
+                            splitk_reduce_kernel<T>, blocks, 256, stream, static_cast<const float*>(e.scratch), splits,
+                            e.slab_floats, m_tiles, n_tiles, bn, static_cast<int>(rows), static_cast<int>(H), e.out, H);
+                        LCE_COUNT_LAUNCH();
+                        return cuda_failed(err) ? LCE_ERR_CUDA : LCE_OK;
+                    };
+                    if ((rc = sum_slices(e1, p.dx_splits, nr))) return rc;
+                    if ((rc = sum_slices(e2, p.dw_splits, nc))) return rc;
+                    both_done = true;
+                }
+            }
+            if (both_done) continue;
             // ---- step 2: dX[r0 : r0+nr, :] (+)= G @ W[c0 : c0+nc, :]
             if (need_dx) {
                 typename EpiStore<TDx>::Params ep;
