@@ -569,3 +569,35 @@ def test_very_small_problems_run_the_forward_in_one_launch(shape, reduction):
             again = ops.linear_cross_entropy(x, w, t, reduction=reduction)
         assert torch.equal(first, again)
         assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(16, 512, 1024), (128, 1024, 8192), (100, 264, 777), (1, 64, 300)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_backward_of_a_handful_of_tokens_computes_dx_and_dw_in_one_launch(shape, dtype):
+    """At most 128 tokens: the recompute launch, then ONE launch that carries both gradient products (plus a sum
+    pass where the long vocabulary contraction of dX was cut into slices). Gradients against autograd of the
+    fp32 expression, and the same bits on a second run."""
+    n, h, v = shape
+    g = torch.Generator().manual_seed(7 * n + h + v)
+    x = torch.randn(n, h, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(v, h, generator=g) / h ** 0.5).to(dtype).to(DEV)
+    t = torch.randint(0, v, (n,), generator=g)
+    if n > 4:
+        t[::7] = -100
+    t = t.to(DEV)
+    go = torch.tensor(0.75, device=DEV)
+    xr = x.float().requires_grad_(True)
+    wr = w.float().requires_grad_(True)
+    z = F.linear(xr, wr)
+    (F.cross_entropy(z, t) * go).backward()
+    lse = torch.logsumexp(z.detach(), dim=-1)
+    L = _lib.lib()
+    dx, dw = ops.linear_cross_entropy_backward(go, x, w, t, lse)
+    torch.cuda.synchronize()
+    before = L.lce_launch_count()
+    dx2, dw2 = ops.linear_cross_entropy_backward(go, x, w, t, lse)
+    torch.cuda.synchronize()
+    assert L.lce_launch_count() - before in (2, 3)  # recompute + both products (+ the slice sum of dX)
+    assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
+    assert scaled_max_err(dx, xr.grad) <= GRAD_RTOL_16BIT and scaled_max_err(dw, wr.grad) <= GRAD_RTOL_16BIT
+    assert _lib.device_status() == 0
