@@ -23,6 +23,12 @@
 // launch, the operand panels they share with their neighbours have left L2 by the time they need them, and
 // DRAM traffic grows to several times the algorithmic bytes.
 //
+// Around the main loop: the kernel sets itself up (barriers, tensor memory, cluster barrier) before it waits for
+// its predecessor in the stream (programmatic dependent launch), so consecutive launches overlap by that much;
+// the epilogue reads tensor memory two chunks deep; an epilogue that has a finish() step can have the LAST CTA to
+// complete run it (a device counter that wraps to zero), which folds a small tail kernel into the launch; and
+// a launch may carry a second, independent product (SecondGemm) whose tiles join the same deal.
+//
 // Two variants, selected by CG:
 //   CG = 1  one CTA per tile: tcgen05.mma.cta_group::1, M = 128. 48 KB per stage (A 16 + B 32).
 //   CG = 2  a CTA PAIR (cluster of 2 on one TPC) per 256 x BN tile: tcgen05.mma.cta_group::2 with
